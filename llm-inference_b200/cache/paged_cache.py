@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from ..csrc.host_module import host
-from ..parts.base import KVCacheSpec, StateSpec
+from ..parts.base import CacheSpecs, KVCacheSpec, StateSpec
 from ..parts.context import CacheView
 
 
@@ -41,10 +41,52 @@ class CacheGroup:
         return self.spec.planes * len(self.entries) * self.spec.kv_heads * self.spec.head_dim * element_size
 
 
+def member_keys(cache_specs: dict) -> dict:
+    """Entries wanted by a mixer made of several mixers: key -> the keys of its members' own
+    entries, ``key + (member,)`` (a plain cache id counts as ``(id,)``), None where a member keeps
+    nothing. A member may itself be made of several."""
+    out: dict = {}
+
+    def walk(key, spec) -> None:
+        if not isinstance(spec, CacheSpecs):
+            return
+        path = key if isinstance(key, tuple) else (key,)
+        out[key] = [None if member is None else path + (j,) for j, member in enumerate(spec.members)]
+        for j, member in enumerate(spec.members):
+            walk(path + (j,), member)
+
+    for cache_id, spec in cache_specs.items():
+        walk(cache_id, spec)
+    return out
+
+
+def flatten_specs(cache_specs: dict) -> dict:
+    """One entry per key: the members of a :class:`CacheSpecs` under ``(cache id, member, ...)``."""
+    flat: dict = {}
+
+    def walk(key, spec) -> None:
+        if isinstance(spec, CacheSpecs):
+            path = key if isinstance(key, tuple) else (key,)
+            for j, member in enumerate(spec.members):
+                if member is not None:
+                    walk(path + (j,), member)
+        else:
+            flat[key] = spec
+
+    for cache_id in sorted(cache_specs):
+        walk(cache_id, cache_specs[cache_id])
+    return flat
+
+
+def _key_order(key) -> tuple:
+    return key if isinstance(key, tuple) else (key, -1)
+
+
 def plan_groups(cache_specs: dict[int, KVCacheSpec | StateSpec]) -> tuple[list[CacheGroup], dict[int, StateSpec]]:
     groups: dict[KVCacheSpec, CacheGroup] = {}
     states: dict[int, StateSpec] = {}
-    for cache_id in sorted(cache_specs):
+    cache_specs = flatten_specs(cache_specs)
+    for cache_id in sorted(cache_specs, key=_key_order):
         spec = cache_specs[cache_id]
         if isinstance(spec, StateSpec):
             states[cache_id] = spec
@@ -107,6 +149,7 @@ class PagedCache:
         self.max_num_sequences = max_num_sequences
         self.max_pages_per_request = math.ceil(max_model_length / page_size)
         self.groups, self.state_specs = plan_groups(cache_specs)
+        self.members = member_keys(cache_specs)
         element = torch.empty((), dtype=dtype).element_size()
         if num_pages is not None:
             for group in self.groups:
@@ -182,6 +225,9 @@ class PagedCache:
             self.manager.fill_tables(request_ids, group.index, out[group.index], self.null_page(group))
 
     def view(self, cache_id: int, writes: bool, block_tables: list[torch.Tensor]) -> CacheView:
+        if cache_id in self.members:
+            views = [None if key is None else self.view(key, writes, block_tables) for key in self.members[cache_id]]
+            return CacheView(cache_id=cache_id, writes=writes, members=views)
         if cache_id in self.states:
             return CacheView(cache_id=cache_id, writes=writes, state=self.states[cache_id])
         group, slot = self.entry_group[cache_id]

@@ -1,4 +1,5 @@
 from .gunedra_config import GunedraConfig
+from .lerorax_config import LeroraxConfig
 from .model_config import ConfigError, ModelConfig, Qwen2Config, read_config_json
 from .registry import (
     Architecture,
@@ -12,6 +13,7 @@ __all__ = [
     "Architecture",
     "ConfigError",
     "GunedraConfig",
+    "LeroraxConfig",
     "ModelConfig",
     "Qwen2Config",
     "parse_config",

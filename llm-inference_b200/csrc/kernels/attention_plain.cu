@@ -51,7 +51,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
                              const int* __restrict__ token_seq,
                              const int* __restrict__ block_table, int max_pages, int num_pages,
                              T* __restrict__ out, int q_heads, int kv_heads, int head_dim,
-                             int page_size, int window, float scale, int* __restrict__ err) {
+                             int page_size, int window, float scale, int value_head, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                  // [head_dim]
   float* probs = qs + head_dim;                                    // [kThreads]
@@ -62,6 +62,8 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
   const int pos = positions[t];
   const int seq = token_seq[t];
   const int kvh = h / (q_heads / kv_heads);
+  // With `value_head` >= 0 every query head's weights meet the values of that one head instead of its own.
+  const int64_t v_shift = value_head >= 0 ? static_cast<int64_t>(value_head - kvh) * page_size * head_dim : 0;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int* table = block_table + static_cast<int64_t>(seq) * max_pages;
 
@@ -106,7 +108,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
         float a = acc[i] * alpha;
         for (int jj = 0; jj < count; ++jj) {
           const int64_t o = offsets[jj];
-          if (o >= 0) a = fmaf(probs[jj], to_f32<T>(v_arena[o + d]), a);
+          if (o >= 0) a = fmaf(probs[jj], to_f32<T>(v_arena[o + v_shift + d]), a);
         }
         acc[i] = a;
       }
@@ -129,7 +131,7 @@ B200_API int b200_paged_attention_plain(const void* q, const void* k_arena, cons
                                         const int* block_table, int max_pages, int num_pages,
                                         void* out, int tokens, int q_heads, int kv_heads,
                                         int head_dim, int page_size, int window, float scale,
-                                        int dtype, int* err, cudaStream_t stream) {
+                                        int value_head, int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
   B200_REQUIRE(tokens > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                "paged_attention_plain: %d query heads over %d kv heads", q_heads, kv_heads);
@@ -138,6 +140,7 @@ B200_API int b200_paged_attention_plain(const void* q, const void* k_arena, cons
                kThreads * kMaxDimsPerThread);
   B200_REQUIRE(q_heads <= 65535, "paged_attention_plain: too many heads");
   B200_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "paged_attention_plain: bad geometry");
+  B200_REQUIRE(value_head < kv_heads, "paged_attention_plain: value head %d of %d", value_head, kv_heads);
   const dim3 grid(tokens, q_heads);
   const size_t smem = sizeof(float) * (head_dim + kThreads) + sizeof(int64_t) * kThreads;
   if (dtype == DTYPE_F32) {
@@ -145,13 +148,13 @@ B200_API int b200_paged_attention_plain(const void* q, const void* k_arena, cons
         static_cast<const float*>(q), static_cast<const float*>(k_arena),
         static_cast<const float*>(v_arena), positions, token_seq, block_table, max_pages,
         num_pages, static_cast<float*>(out), q_heads, kv_heads, head_dim, page_size, window, scale,
-        err);
+        value_head, err);
   } else if (dtype == DTYPE_BF16) {
     paged_attention_plain_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_arena),
         static_cast<const __nv_bfloat16*>(v_arena), positions, token_seq, block_table, max_pages,
         num_pages, static_cast<__nv_bfloat16*>(out), q_heads, kv_heads, head_dim, page_size,
-        window, scale, err);
+        window, scale, value_head, err);
   } else {
     return b200_fail("paged_attention_plain: unknown dtype %d", dtype);
   }

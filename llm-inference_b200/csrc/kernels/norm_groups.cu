@@ -248,6 +248,82 @@ __global__ void poly_norm_vec_kernel(const T* z, const float* __restrict__ coeff
   }
 }
 
+// A layer whose mixer is two mixers side by side: y = (wa (.) a / rms(a) + wb (.) b / rms(b)) / 2 is the mixer's
+// output, and x <- x + w (.) y / rms(y) adds its norm to the stream. One block per row; y stays in shared
+// memory in 32-bit between the two norms. `cast` is the stream rounded once to the compute dtype.
+template <typename T>
+__global__ void pair_norm_add_kernel(const float* in_x, const T* a, const T* b, const float* __restrict__ wa,
+                                     const float* __restrict__ wb, const float* __restrict__ weight, int hidden, float eps_pair,
+                                     float eps, float* out_x, T* cast) {
+  extern __shared__ float pair_y[];  // [hidden]
+  __shared__ float scratch[32];
+  wait_for_predecessor();
+  let_successor_start();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * hidden;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float av = to_f32<T>(a[row + i]), bv = to_f32<T>(b[row + i]);
+    sa = fmaf(av, av, sa);
+    sb = fmaf(bv, bv, sb);
+  }
+  const float n = static_cast<float>(hidden);
+  const float ra = 1.f / sqrtf(block_sum(sa, scratch) / n + eps_pair);
+  const float rb = 1.f / sqrtf(block_sum(sb, scratch) / n + eps_pair);
+  float sy = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float y = 0.5f * (to_f32<T>(a[row + i]) * ra * wa[i] + to_f32<T>(b[row + i]) * rb * wb[i]);
+    pair_y[i] = y;
+    sy = fmaf(y, y, sy);
+  }
+  const float ry = 1.f / sqrtf(block_sum(sy, scratch) / n + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = in_x[row + i] + pair_y[i] * ry * weight[i];
+    out_x[row + i] = v;
+    if (cast) cast[row + i] = from_f32<T>(v);
+  }
+}
+
+// x[t] = table[ids[t]] + pairs[row(t)] in 32-bit, row(t) = (previous * mul_prev + ids[t] * mul_cur) mod buckets with
+// `previous` the token in front of t in its request, or row `buckets` (the table's last) for a request's first
+// token. The token in front of a step's first one comes from the request's slot in `last_token`.
+template <typename T>
+__global__ void embedding_bigram_kernel(const T* __restrict__ table, const T* __restrict__ pairs, const int* ids,
+                                        const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_slot, const int* last_token,
+                                        int buckets, int64_t mul_prev, int64_t mul_cur, float* out, T* cast, int hidden, int vocab,
+                                        int* err) {
+  wait_for_predecessor();
+  let_successor_start();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_TOKEN);
+  const int seq = token_seq[t];
+  int64_t pair_row = buckets;
+  if (positions[t] > 0) {
+    const int previous = t > seq_q_start[seq] ? ids[t - 1] : last_token[seq_slot[seq]];
+    pair_row = (static_cast<int64_t>(previous) * mul_prev + static_cast<int64_t>(id) * mul_cur) % buckets;
+    if (pair_row < 0) pair_row += buckets;
+  }
+  const T* src = table + static_cast<int64_t>(bad ? 0 : id) * hidden;
+  const T* add = pairs + pair_row * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = bad ? 0.f : to_f32<T>(src[i]) + to_f32<T>(add[i]);
+    out[static_cast<int64_t>(t) * hidden + i] = v;
+    if (cast) cast[static_cast<int64_t>(t) * hidden + i] = from_f32<T>(v);
+  }
+}
+
+// Each request's slot takes the step's last token of the request.
+__global__ void last_token_update_kernel(const int* ids, const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                                         const int* __restrict__ seq_slot, int seqs, int* last_token) {
+  wait_for_predecessor();
+  let_successor_start();
+  const int seq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (seq >= seqs || seq_q_len[seq] <= 0) return;
+  last_token[seq_slot[seq]] = ids[seq_q_start[seq] + seq_q_len[seq] - 1];
+}
+
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 int row_threads(int hidden) { return hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128); }
@@ -353,4 +429,50 @@ B200_API int b200_poly_norm(const void* z, const float* coefficients, int rows, 
     return b200_fail("poly_norm: unknown dtype %d", dtype);
   }
   return b200_check_launch("poly_norm");
+}
+
+B200_API int b200_pair_norm_add(const float* in_x, const void* a, const void* b, const float* wa, const float* wb, const float* weight,
+                                int rows, int hidden, float eps_pair, float eps, float* out_x, void* cast, int dtype,
+                                cudaStream_t stream) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(rows > 0 && hidden > 0 && hidden <= 48 * 1024, "pair_norm_add: bad sizes");
+  const int threads = row_threads(hidden);
+  const size_t smem = sizeof(float) * hidden;
+  auto launch = [&](auto kernel, auto* pa, auto* pb, auto* pc) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, in_x, pa, pb, wa, wb, weight, hidden, eps_pair, eps, out_x, pc);
+  };
+  if (dtype == DTYPE_F32)
+    launch(pair_norm_add_kernel<float>, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(cast));
+  else if (dtype == DTYPE_BF16)
+    launch(pair_norm_add_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+           static_cast<__nv_bfloat16*>(cast));
+  else
+    return b200_fail("pair_norm_add: unknown dtype %d", dtype);
+  return b200_check_launch("pair_norm_add");
+}
+
+B200_API int b200_embedding_bigram(const void* table, const void* pairs, const int* ids, const int* positions, const int* token_seq,
+                                   const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int* last_token, int buckets,
+                                   int64_t mul_prev, int64_t mul_cur, float* out, void* cast, int tokens, int seqs, int hidden, int vocab,
+                                   int dtype, int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  B200_REQUIRE(tokens > 0 && seqs > 0 && hidden > 0 && vocab > 0 && buckets > 0, "embedding_bigram: bad sizes");
+  const int threads = row_threads(hidden);
+  if (dtype == DTYPE_F32) {
+    launch_kernel(embedding_bigram_kernel<float>, dim3(tokens), dim3(threads), 0, stream, static_cast<const float*>(table),
+                  static_cast<const float*>(pairs), ids, positions, token_seq, seq_q_start, seq_slot, static_cast<const int*>(last_token),
+                  buckets, mul_prev, mul_cur, out, static_cast<float*>(cast), hidden, vocab, err);
+  } else if (dtype == DTYPE_BF16) {
+    launch_kernel(embedding_bigram_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(table),
+                  static_cast<const __nv_bfloat16*>(pairs), ids, positions, token_seq, seq_q_start, seq_slot,
+                  static_cast<const int*>(last_token), buckets, mul_prev, mul_cur, out, static_cast<__nv_bfloat16*>(cast), hidden, vocab,
+                  err);
+  } else {
+    return b200_fail("embedding_bigram: unknown dtype %d", dtype);
+  }
+  if (int status = b200_check_launch("embedding_bigram")) return status;
+  launch_kernel(last_token_update_kernel, dim3((seqs + 127) / 128), dim3(128), 0, stream, ids, seq_q_start, seq_q_len, seq_slot, seqs,
+                last_token);
+  return b200_check_launch("last_token_update");
 }

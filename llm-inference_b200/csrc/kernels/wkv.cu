@@ -197,10 +197,11 @@ wkv_recurrence_kernel(const float* r, const float* k, const float* v, const floa
   }
 }
 
-// out[t, h, :] = o / rms(o) * weight[h, :] * silu(gate[t, h, :]); one warp per (token, head).
+// out[t, h, :] = o / rms(o) * weight[h, :] * act(gate[t, h, :]), act = silu, or sigmoid with `sigmoid_gate`; one warp
+// per (token, head). Gate rows are `gate_ld` numbers apart.
 template <typename T>
-__global__ void wkv_output_kernel(const float* o, const float* __restrict__ weight, const T* gate, int rows, int heads, int dv,
-                                  float eps, T* out) {
+__global__ void wkv_output_kernel(const float* o, const float* __restrict__ weight, const T* gate, int gate_ld, int rows, int heads,
+                                  int dv, float eps, int sigmoid_gate, T* out) {
   wait_for_predecessor();
   let_successor_start();
   const int lane = threadIdx.x & 31;
@@ -212,11 +213,11 @@ __global__ void wkv_output_kernel(const float* o, const float* __restrict__ weig
   for (int i = lane; i < dv; i += 32) ss = fmaf(src[i], src[i], ss);
   ss = warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / static_cast<float>(dv) + eps);
-  const T* g = gate + item * dv;
+  const T* g = gate + (item / heads) * gate_ld + h * dv;
   T* dst = out + item * dv;
   for (int i = lane; i < dv; i += 32) {
     const float gv = to_f32<T>(g[i]);
-    dst[i] = from_f32<T>(src[i] * inv * weight[h * dv + i] * (gv * sigmoid_f(gv)));
+    dst[i] = from_f32<T>(src[i] * inv * weight[h * dv + i] * (sigmoid_gate ? sigmoid_f(gv) : gv * sigmoid_f(gv)));
   }
 }
 
@@ -314,19 +315,19 @@ B200_API int b200_wkv_recurrence(const float* r, const float* k, const float* v,
   return b200_check_launch("wkv_recurrence");
 }
 
-B200_API int b200_wkv_output(const float* o, const float* weight, const void* gate, int rows, int heads, int dv, float eps, void* out,
-                             int dtype, cudaStream_t stream) {
+B200_API int b200_wkv_output(const float* o, const float* weight, const void* gate, int gate_ld, int rows, int heads, int dv, float eps,
+                             int sigmoid_gate, void* out, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  B200_REQUIRE(rows > 0 && heads > 0 && dv > 0, "wkv_output: bad sizes");
+  B200_REQUIRE(rows > 0 && heads > 0 && dv > 0 && gate_ld >= heads * dv, "wkv_output: bad sizes");
   const int threads = 128;
   const int64_t items = static_cast<int64_t>(rows) * heads;
   const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
   if (dtype == DTYPE_F32) {
-    launch_kernel(wkv_output_kernel<float>, dim3(blocks), dim3(threads), 0, stream, o, weight, static_cast<const float*>(gate), rows,
-                  heads, dv, eps, static_cast<float*>(out));
+    launch_kernel(wkv_output_kernel<float>, dim3(blocks), dim3(threads), 0, stream, o, weight, static_cast<const float*>(gate), gate_ld,
+                  rows, heads, dv, eps, sigmoid_gate, static_cast<float*>(out));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(wkv_output_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, o, weight,
-                  static_cast<const __nv_bfloat16*>(gate), rows, heads, dv, eps, static_cast<__nv_bfloat16*>(out));
+                  static_cast<const __nv_bfloat16*>(gate), gate_ld, rows, heads, dv, eps, sigmoid_gate, static_cast<__nv_bfloat16*>(out));
   } else {
     return b200_fail("wkv_output: unknown dtype %d", dtype);
   }

@@ -55,7 +55,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_paged_attention_plain": [c_void_p] * 6
     + [c_int, c_int, c_void_p]
     + [c_int] * 6
-    + [c_float, c_int, c_void_p, c_void_p],
+    + [c_float, c_int, c_int, c_void_p, c_void_p],
     "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
     "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "b200_paged_decode_attention_tma": [c_void_p] * 8 + [c_int] * 8 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -92,7 +92,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_tanh_rows": [c_void_p, c_int64, c_int, c_void_p],
     "b200_wkv_prepare": [c_void_p] * 6 + [c_int] * 3 + [c_void_p] * 5 + [c_int, c_void_p],
     "b200_wkv_recurrence": [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 3,
-    "b200_wkv_output": [c_void_p] * 3 + [c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_wkv_output": [c_void_p] * 3 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
     "b200_norm_kv_write": [c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_int] + [c_void_p] * 5 + [c_int] * 9 + [c_float, c_int, c_int,
                            c_void_p, c_void_p],
     "b200_head_gate": [c_void_p, c_void_p] + [c_int] * 6 + [c_void_p, c_int, c_void_p],
@@ -104,6 +104,14 @@ _SIGNATURES: dict[str, list] = {
     "b200_moe_product_tcgen05": [c_void_p] * 5 + [c_int] * 7 + [c_float, c_void_p, c_int, c_void_p, c_void_p],
     "b200_moe_combine": [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_void_p],
     "b200_clamped_glu": [c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_mingru": [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 4 + [c_void_p] * 3 + [c_int, c_void_p],
+    "b200_delta_general_prepare": [c_void_p] + [c_int] * 5 + [c_void_p] * 3 + [c_int] * 3 + [c_void_p] * 6 + [c_int, c_void_p],
+    "b200_delta_general_recurrence": [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 3,
+    "b200_conv_norm_rope_write": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int]
+                                 + [c_void_p] * 7 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 10 + [c_void_p, c_void_p],
+    "b200_mix_heads_gate": [c_void_p] * 3 + [c_int] * 6 + [c_void_p, c_int, c_void_p],
+    "b200_pair_norm_add": [c_void_p] * 6 + [c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_embedding_bigram": [c_void_p] * 9 + [c_int, c_int64, c_int64, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_void_p],
 }
 
 
@@ -142,6 +150,8 @@ class KernelLibrary:
         self.lib.b200_moe_mma_supported.restype = c_int
         self.lib.b200_moe_tcgen05_supported.argtypes = [c_int, c_int]
         self.lib.b200_moe_tcgen05_supported.restype = c_int
+        self.lib.b200_mingru_scratch.argtypes = [c_int] * 3
+        self.lib.b200_mingru_scratch.restype = c_int64
         self.lib.b200_skinny_gemm_fold_parts.argtypes = [c_int, c_int]
         self.lib.b200_skinny_gemm_fold_parts.restype = c_int
         self.lib.b200_stream_gemm_fold_parts.argtypes = [c_int, c_int, c_int]

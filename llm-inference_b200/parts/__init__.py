@@ -1,5 +1,6 @@
-from . import attention, block, delta_rule, embedding, feed_forward, gated_attention, hyper, latent_attention, norms, positions, wkv  # noqa: F401  (register parts)
+from . import attention, block, delta_rule, embedding, feed_forward, gated_attention, hyper, latent_attention, mingru, mixed_attention, norms, parallel, positions, wkv  # noqa: F401  (register parts)
 from .base import (
+    CacheSpecs,
     KVCacheSpec,
     Part,
     PartSpec,
@@ -12,6 +13,7 @@ from .context import CacheView, HostBatch, StepContext, Workspace
 from .model import LayerCall, Model, ModelRecipe
 
 __all__ = [
+    "CacheSpecs",
     "CacheView",
     "HostBatch",
     "KVCacheSpec",

@@ -27,17 +27,21 @@ def attend(
     kv_heads: int,
     head_dim: int,
     scale: float,
+    value_head: int = -1,
 ) -> None:
+    """``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
+    instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head)."""
     choice = ctx.options.get("attention", "auto")
     tuned = (
         choice != "plain"
+        and value_head < 0
         and q.dtype == torch.bfloat16
         and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=False)
     )
     if not tuned:
         if choice in ("flash", "tcgen05"):
             raise ops.KernelError("the tensor-core attention kernels do not take this shape or dtype")
-        ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale)
+        ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale, value_head=value_head)
         return
     decode_seqs = ctx.num_decode_seqs
     if decode_seqs and not ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=True):

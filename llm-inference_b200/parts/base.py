@@ -16,11 +16,13 @@ Kinds of part and what each must provide:
                   projection bias, encodes each token's position into its queries and keys,
                   writes keys and values to the token's page and the queries to ``q_out``; the
                   mixer never looks inside (the rotary part does it in one fused kernel).
-``mixer``         ``cache_spec() -> KVCacheSpec | StateSpec | None`` and
+``mixer``         ``cache_spec() -> KVCacheSpec | StateSpec | CacheSpecs | None`` and
                   ``forward(ctx, cache, h) -> Tensor`` where ``cache`` is the
                   :class:`CacheView` of the layer call.
 ``feed_forward``  ``forward(ctx, h) -> Tensor``.
-``embedding``     ``forward(ctx) -> Tensor`` (the 32-bit residual stream of the new tokens).
+``embedding``     ``forward(ctx) -> Tensor`` (the 32-bit residual stream of the new tokens). An
+                  embedding that carries something from step to step (the token in front) also
+                  has ``cache_spec() -> StateSpec`` and takes ``forward(ctx, cache)``.
 ``head``          ``forward(ctx, h) -> Tensor`` (32-bit logits of the given rows).
 ``block``         ``forward(ctx, cache, x, delta) -> Tensor``: one layer's arrangement of the
                   parts above; returns the branch output still to be added to ``x``.
@@ -56,6 +58,15 @@ class StateSpec:
 
     shapes: tuple[tuple[int, ...], ...]
     dtypes: tuple[torch.dtype, ...]
+
+
+@dataclass(frozen=True)
+class CacheSpecs:
+    """What a mixer made of several mixers wants: one cache entry per member, in the members'
+    order (None for a member that keeps nothing). The layer call's :class:`CacheView` then holds
+    one view per member in ``members``."""
+
+    members: tuple["KVCacheSpec | StateSpec | None", ...]
 
 
 @dataclass(frozen=True)

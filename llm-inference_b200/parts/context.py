@@ -44,7 +44,8 @@ class CacheView:
     ``[pages, kv_heads, page_size, head_dim]`` and ``block_table`` is ``[S, max_pages]``
     (int32, on the device). For per-request state: ``state`` is the list of slot arrays
     ``[slots, *shape]``. ``writes`` is false when the call only reads a cache that another
-    layer call fills.
+    layer call fills. For a mixer made of several mixers ``members`` holds one view per member
+    (None where a member keeps nothing).
     """
 
     cache_id: int
@@ -57,6 +58,7 @@ class CacheView:
     page_size: int = 0
     window: int = 0
     state: list[torch.Tensor] | None = None
+    members: list | None = None
 
 
 class Workspace:

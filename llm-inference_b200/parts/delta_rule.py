@@ -105,4 +105,66 @@ class ChannelDeltaRule(Part):
         return ops.linear(ctx, y, self.w_o, ctx.buffer("branch", (t, self.hidden_size)))
 
 
+class GeneralDeltaRule(Part):
+    """Per head a state ``S [dim, dim]`` (32-bit, zero at a request's start) is carried from token to token:
+    ``S <- diag(w) S - (a * u) (u^T S) + k v^T`` (both terms read the old state), ``o = S^T r`` (the new one), with
+    ``u = k / sqrt(sum k^2 + 1e-6)`` the key's direction per head.
+
+    ``r, k, v`` (``heads x dim`` each) are projections of ``h`` without biases;
+    ``w = exp(-e^(-1/2) * sigmoid(W_w2 tanh(W_w1 h) + w0))`` is the decay and ``a = sigmoid(W_a h + b_a)`` the share
+    removed, both per head and key channel. Each head's ``o`` is divided by its root mean square, times ``norm``
+    (all heads' size), times ``sigmoid(W_g h)``; then ``W_o``. The inner size of the decay's low-rank pair
+    (``decay_rank``) is the checkpoint's; a configuration names it only to draw random weights.
+
+    Per-request state: ``S``. Two matrix products read ``h``: ``[r | k | v | a | g]`` and ``w1``; the second small
+    product has a 32-bit result. Decays, shares, directions and the recurrence are 32-bit. Tensor names:
+    ``prefix + r | k | v | a | a.b | g | w1 | w2 | w0 | norm | o``."""
+
+    def __init__(self, *, prefix: str, hidden_size: int, heads: int, dim: int, eps: float, decay_rank: int | None = None,
+                 out_name: str = "branch") -> None:
+        self.prefix, self.hidden_size, self.heads, self.dim, self.eps = prefix, hidden_size, int(heads), int(dim), float(eps)
+        self.decay_rank = -1 if decay_rank is None else int(decay_rank)
+        self.out_name = out_name
+        self.w_main = self.w_low = self.w_high = self.w_o = self.w0 = self.a_bias = self.norm_weight = None
+
+    def cache_spec(self) -> StateSpec:
+        return StateSpec(((self.heads, self.dim, self.dim),), (torch.float32,))
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, d, inner = self.prefix, self.hidden_size, self.heads * self.dim
+        specs = [TensorSpec(p + s, (inner, d)) for s in ("r", "k", "v", "a", "g")]
+        return specs + [
+            TensorSpec(p + "a.b", (inner,)), TensorSpec(p + "w1", (self.decay_rank, d)), TensorSpec(p + "w2", (inner, self.decay_rank)),
+            TensorSpec(p + "w0", (inner,)), TensorSpec(p + "norm", (inner,), init="one_plus_normal"), TensorSpec(p + "o", (d, inner)),
+        ]
+
+    def load(self, tensors, dtype, device) -> None:
+        p, f32 = self.prefix, torch.float32
+
+        def get(name: str, to=dtype) -> torch.Tensor:
+            return tensors[p + name].to(device=device, dtype=to).contiguous()
+
+        self.w_main = torch.cat([get(s) for s in ("r", "k", "v", "a", "g")]).contiguous()
+        self.w_low, self.w_high, self.w_o = get("w1"), get("w2"), get("o")
+        self.w0, self.a_bias, self.norm_weight = get("w0", f32), get("a.b", f32), get("norm", f32)
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_main, self.w_low, self.w_high, self.w_o))
+
+    def forward(self, ctx: StepContext, cache: CacheView, h: torch.Tensor) -> torch.Tensor:
+        t, heads, dim = ctx.num_tokens, self.heads, self.dim
+        inner = heads * dim
+        f32 = torch.float32
+        main = ops.linear(ctx, h, self.w_main, ctx.buffer("gdelta_main", (t, 5 * inner)))
+        low = ops.linear(ctx, h, self.w_low, ctx.buffer("gdelta_low", (t, self.w_low.shape[0])))
+        low = ops.tanh_rows(ctx, low)
+        log_decay = ops.linear(ctx, low, self.w_high, ctx.buffer("gdelta_log_decay", (t, inner), f32))
+        outs = tuple(ctx.buffer("gdelta_" + name, (t, inner), f32) for name in ("r", "k", "v", "w", "au", "u"))
+        ops.delta_general_prepare(ctx, main, (0, inner, 2 * inner, 3 * inner), log_decay, self.w0, self.a_bias, heads, dim, outs)
+        o = ops.delta_general_recurrence(ctx, *outs, cache.state[0], ctx.buffer("gdelta_o", (t, inner), f32), heads, dim, dim)
+        y = ops.wkv_output(ctx, o, self.norm_weight, main[:, 4 * inner:], heads, dim, self.eps, ctx.buffer("attn", (t, inner)), sigmoid_gate=True)
+        return ops.linear(ctx, y, self.w_o, ctx.buffer(self.out_name, (t, self.hidden_size)))
+
+
 register_part("mixer", "channel_delta", ChannelDeltaRule)
+register_part("mixer", "general_delta", GeneralDeltaRule)

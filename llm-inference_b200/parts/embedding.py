@@ -6,7 +6,7 @@ import torch
 
 from ..weights.loader import TensorSpec
 from . import ops
-from .base import Part, register_part
+from .base import Part, StateSpec, register_part
 from .context import StepContext
 
 
@@ -74,6 +74,40 @@ class SinusoidEmbedding(Part):
         return ops.embedding_sinusoid(ctx, self.table, self.inv_freq, self.scale, self.streams, x)
 
 
+class BigramEmbedding(Part):
+    """``x[t] = table[token[t]] + pairs[r(t)]`` in 32-bit, where ``r(t) = (previous * mul_prev + token * mul_cur) mod
+    buckets`` hashes the token together with the one in front of it in its request; a request's first token
+    takes the pair table's last row (number ``buckets``). The token in front of a step's first one is
+    per-request state (one int32 per slot). With ``cast`` the step also gets the stream rounded to the compute
+    dtype (buffer ``stream_cast``)."""
+
+    def __init__(self, *, name: str, pairs_name: str, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int, mul_cur: int,
+                 cast: bool = False) -> None:
+        self.name, self.pairs_name, self.vocab_size, self.hidden_size = name, pairs_name, vocab_size, hidden_size
+        self.buckets, self.mul_prev, self.mul_cur, self.cast = int(buckets), int(mul_prev), int(mul_cur), bool(cast)
+        self.table: torch.Tensor | None = None
+        self.pairs: torch.Tensor | None = None
+
+    def cache_spec(self) -> StateSpec:
+        return StateSpec(((1,),), (torch.int32,))
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size)), TensorSpec(self.pairs_name, (self.buckets + 1, self.hidden_size))]
+
+    def load(self, tensors, dtype, device) -> None:
+        self.table = tensors[self.name].to(device=device, dtype=dtype).contiguous()
+        self.pairs = tensors[self.pairs_name].to(device=device, dtype=dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        return 0  # a step reads only its tokens' rows
+
+    def forward(self, ctx: StepContext, cache) -> torch.Tensor:
+        x = ctx.buffer("residual", (ctx.num_tokens, self.hidden_size), torch.float32)
+        rounded = self.cast and self.table.dtype != torch.float32  # in 32-bit the stream is its own copy
+        cast = ctx.buffer("stream_cast", (ctx.num_tokens, self.hidden_size), self.table.dtype) if rounded else None
+        return ops.embedding_bigram(ctx, self.table, self.pairs, cache.state[0], self.buckets, self.mul_prev, self.mul_cur, x, cast)
+
+
 class OutputHead(Part):
     """``logits = h W^T`` in 32-bit. With ``tied_to`` the matrix is the embedding table and
     the checkpoint need not hold a tensor of its own (python/instinct/export.py:38-41)."""
@@ -110,4 +144,5 @@ class OutputHead(Part):
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "sinusoid_embedding", SinusoidEmbedding)
+register_part("embedding", "bigram_embedding", BigramEmbedding)
 register_part("head", "linear_head", OutputHead)

@@ -82,6 +82,34 @@ class PolyNormFeedForward(Part):
         return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
 
 
+class ClampedGLU(Part):
+    """``down(y)`` with ``g = min(gate(h), limit)``, ``u = clamp(up(h), -limit, limit)``, ``y = g * sigmoid(1.702 g) * (u + 1)``,
+    no biases. The gate and up matrices are one ``[2 * intermediate, hidden]`` matrix (gate rows first), so one
+    product gives both. Tensor names: ``prefix + gate | up | down``."""
+
+    def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int, limit: float) -> None:
+        self.prefix, self.hidden_size, self.intermediate_size, self.limit = prefix, hidden_size, int(intermediate_size), float(limit)
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+        return [TensorSpec(p + "gate", (i, h)), TensorSpec(p + "up", (i, h)), TensorSpec(p + "down", (h, i))]
+
+    def load(self, tensors, dtype, device) -> None:
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors[p + "gate"].to(device=device, dtype=dtype), tensors[p + "up"].to(device=device, dtype=dtype)]).contiguous()
+        self.w_down = tensors[p + "down"].to(device=device, dtype=dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        t, i = ctx.num_tokens, self.intermediate_size
+        gate_up = ops.linear(ctx, h, self.w_gate_up, ctx.buffer("gate_up", (t, 2 * i)))
+        act = ops.clamped_glu(ctx, gate_up, self.limit, ctx.buffer("act", (t, i)))
+        return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
+
+
 class RoutedExperts(Part):
     """A mixture of ``experts`` small gated feed-forward layers of which each token uses ``top``, plus an
     optional shared expert that every token uses.
@@ -159,3 +187,4 @@ class RoutedExperts(Part):
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "poly_norm", PolyNormFeedForward)
 register_part("feed_forward", "routed_experts", RoutedExperts)
+register_part("feed_forward", "clamped_glu", ClampedGLU)

@@ -28,6 +28,9 @@ def _no_range(name: str):
     yield
 
 
+EMBEDDING_CACHE = -1  # the cache entry of an embedding that keeps per-request state
+
+
 @dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order: run ``layer`` against cache entry ``cache``.
@@ -82,6 +85,7 @@ class Model:
                 raise ValueError(f"the run order names layer {call.layer}, which does not exist")
         self.dtype: torch.dtype | None = None
         self.device: torch.device | None = None
+        self._ids = None
         self.graph_safe = all(
             p.graph_safe for p in (self.embedding, *self.blocks, self.final_norm, self.head)
         )
@@ -117,6 +121,9 @@ class Model:
     def cache_specs(self) -> dict[int, KVCacheSpec | StateSpec]:
         """Cache entry id -> what its owner (the call that writes it) needs."""
         specs: dict[int, KVCacheSpec | StateSpec] = {}
+        own = getattr(self.embedding, "cache_spec", None)
+        if own is not None and own() is not None:
+            specs[EMBEDDING_CACHE] = own()  # what the embedding carries from step to step
         for call in self.schedule:
             spec = self.blocks[call.layer].cache_spec()
             if spec is None:
@@ -130,6 +137,11 @@ class Model:
             if spec is not None and not call.writes and call.cache_id not in specs:
                 raise ValueError(f"layer {call.layer} reads cache entry {call.cache_id}, which nobody writes")
         return specs
+
+    def _cache_ids(self):
+        if self._ids is None:
+            self._ids = frozenset(self.cache_specs())
+        return self._ids
 
     # -- the forward pass of one step --------------------------------------------------------
 
@@ -147,7 +159,10 @@ class Model:
         if resident is not None and resident.takes(ctx):
             with mark("resident step"):
                 return resident.run(ctx, cache_views)
-        x = self.embedding.forward(ctx)
+        if EMBEDDING_CACHE in self._cache_ids():
+            x = self.embedding.forward(ctx, cache_views(LayerCall(-1, EMBEDDING_CACHE)))
+        else:
+            x = self.embedding.forward(ctx)
         delta = None
         for index, call in enumerate(self.schedule):
             block = self.blocks[call.layer]

@@ -66,17 +66,22 @@ class GroupedRMSNorm(Part):
 
     foldable = False
 
-    def __init__(self, *, name: str, hidden_size: int, groups: int, eps: float) -> None:
+    def __init__(self, *, name: str, hidden_size: int, groups: int, eps: float, around_zero: bool = False) -> None:
         if groups <= 0 or hidden_size % groups:
             raise ValueError(f"{hidden_size} columns do not cut into {groups} equal groups")
         self.name, self.hidden_size, self.groups, self.eps = name, hidden_size, int(groups), float(eps)
+        # around_zero: the checkpoint stores the weight as an offset from one (the factor is 1 + w); one is
+        # added once, in 32-bit, when the weights are loaded.
+        self.around_zero = bool(around_zero)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.name, (self.hidden_size,), init="one_plus_normal")]
+        return [TensorSpec(self.name, (self.hidden_size,), init="normal" if self.around_zero else "one_plus_normal")]
 
     def load(self, tensors, dtype, device) -> None:
         self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+        if self.around_zero:
+            self.weight += 1.0
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * 4
@@ -91,6 +96,12 @@ class GroupedRMSNorm(Part):
 
     def add_branch(self, ctx: StepContext, x_in: torch.Tensor, branch: torch.Tensor, scale: torch.Tensor | None, mult: float,
                    x_out: torch.Tensor, **more) -> None:
+        if isinstance(branch, ops.BranchPair):
+            # two mixers side by side: their combination and this norm are one kernel
+            if self.groups != 1 or scale is not None or mult != 1.0 or any(v is not None for k, v in more.items() if k != "cast"):
+                raise ValueError("a pair of branch outputs is added by a plain RMS norm without scale, multiplier or depth average")
+            ops.pair_norm_add(ctx, x_in, branch, self.weight, self.eps, x_out, cast=more.get("cast"))
+            return
         ops.branch_norm_add(ctx, x_in, branch, self.weight, scale, mult, self.groups, self.eps, x_out, **more)
 
 

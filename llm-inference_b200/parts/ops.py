@@ -359,8 +359,10 @@ def paged_attention_plain(
     *,
     first_token: int = 0,
     num_tokens: int | None = None,
+    value_head: int = -1,
 ) -> torch.Tensor:
-    """Attention of rows ``first_token .. first_token + num_tokens`` of the step over the cache."""
+    """Attention of rows ``first_token .. first_token + num_tokens`` of the step over the cache. With
+    ``value_head`` >= 0 every query head's weights are applied to the values of that kv head."""
     tokens = ctx.num_tokens - first_token if num_tokens is None else num_tokens
     if tokens <= 0:
         return out
@@ -375,7 +377,7 @@ def paged_attention_plain(
         ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
         ptr(out) if first_token == 0 else _offset(out, first_token * row_bytes),
         c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size),
-        c_int(cache.window), c_float(scale), c_int(dtype_code(q.dtype)), ptr(ctx.err), ctx.stream,
+        c_int(cache.window), c_float(scale), c_int(value_head), c_int(dtype_code(q.dtype)), ptr(ctx.err), ctx.stream,
     )
     return out
 
@@ -907,15 +909,17 @@ def wkv_recurrence(
     return out
 
 
-def wkv_output(ctx: StepContext, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, heads: int, dv: int, eps: float, out: torch.Tensor) -> torch.Tensor:
-    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight[h] * silu(gate[t, h])``."""
+def wkv_output(ctx: StepContext, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, heads: int, dv: int, eps: float, out: torch.Tensor,
+               sigmoid_gate: bool = False) -> torch.Tensor:
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight[h] * silu(gate[t, h])`` (``sigmoid`` instead of ``silu`` with
+    ``sigmoid_gate``); ``gate`` may be a column slice of a wider buffer."""
     rows = o.shape[0]
     _need(o.dtype == torch.float32 and o.is_contiguous() and tuple(out.shape) == (rows, heads * dv) and out.is_contiguous(), "wkv_output: bad operands")
-    _need(tuple(gate.shape) == (rows, heads * dv) and gate.is_contiguous() and gate.dtype == out.dtype, "wkv_output: bad gate")
+    _need(gate.stride(1) == 1 and gate.shape[1] == heads * dv and gate.dtype == out.dtype, "wkv_output: bad gate")
     _need(weight.dtype == torch.float32 and weight.numel() == heads * dv, "wkv_output: weight must be float32 [heads * dv]")
     ctx.lib.call(
-        "b200_wkv_output", ptr(o), ptr(weight), ptr(gate), c_int(rows), c_int(heads), c_int(dv), c_float(eps), ptr(out),
-        c_int(dtype_code(out.dtype)), ctx.stream,
+        "b200_wkv_output", ptr(o), ptr(weight), ptr(gate), c_int(gate.stride(0)), c_int(rows), c_int(heads), c_int(dv), c_float(eps),
+        c_int(1 if sigmoid_gate else 0), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream,
     )
     return out
 
@@ -1056,4 +1060,163 @@ def clamped_glu(ctx: StepContext, gate_up: torch.Tensor, limit: float, out: torc
     ff = twice // 2
     _need(twice == 2 * ff and tuple(out.shape) == (rows, ff) and gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "clamped_glu: bad operands")
     ctx.lib.call("b200_clamped_glu", ptr(gate_up), c_int(rows), c_int(ff), c_float(limit), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream)
+    return out
+
+
+# -- minGRU, the generalized delta rule, attention with weights mixed over heads, a pair of mixers, bigram embedding --
+
+
+@dataclass
+class BranchPair:
+    """The outputs of two mixers that ran side by side, not yet combined: the layer's result is
+    ``(wa * a / rms(a) + wb * b / rms(b)) / 2``. The norm that adds it into the stream combines them."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+    wa: torch.Tensor
+    wb: torch.Tensor
+    eps: float
+
+
+MINGRU_PIECE = 64  # tokens per piece of the three-pass form (csrc/kernels/mingru.cu)
+
+
+def mingru(ctx: StepContext, proj: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``proj`` rows are ``[pz | px | pg]``; ``bias`` is ``[bz | bx]`` (float32); ``state`` the slots ``[slots, width]``.
+    Steps whose longest run has more than two pieces of tokens run their prompt portions in three passes
+    (pieces at the same time), everything else in one pass per request."""
+    tokens, width = out.shape
+    _need(proj.is_contiguous() and proj.shape == (tokens, 3 * width) and out.is_contiguous() and out.dtype == proj.dtype, "mingru: bad operands")
+    _need(bias.dtype == torch.float32 and bias.numel() == 2 * width and bias.is_contiguous(), "mingru: the biases are float32 [2 * width]")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (width,) and state.is_contiguous(), "mingru: the state is float32 [slots, width]")
+    first_long = ctx.num_seqs
+    maps = None
+    if ctx.max_q_len > 2 * MINGRU_PIECE and not ctx.captured:
+        first_long = ctx.num_decode_seqs
+        count = int(ctx.lib.lib.b200_mingru_scratch(ctx.num_seqs - first_long, ctx.max_q_len, width))
+        maps = ctx.buffer("mingru_maps", (count,), torch.float32, per_token=False)
+    ctx.lib.call(
+        "b200_mingru", ptr(proj), c_int(proj.stride(0)), ptr(bias), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_slot),
+        c_int(first_long), c_int(ctx.num_seqs), c_int(max(ctx.max_q_len, 1)), c_int(width), ptr(state), ptr(maps), ptr(out),
+        c_int(dtype_code(proj.dtype)), ctx.stream,
+    )
+    if maps is not None:
+        ctx.lib.calls += 2 + (1 if first_long else 0)
+    return out
+
+
+def delta_general_prepare(
+    ctx: StepContext, proj: torch.Tensor, offsets: tuple[int, int, int, int], log_decay: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+    heads: int, dim: int, outs: tuple[torch.Tensor, ...],
+) -> None:
+    """From ``proj`` (columns r, k, v, a at ``offsets``) and the decay's low-rank image ``log_decay`` (float32):
+    the 32-bit r, k, v, ``w = exp(-e^(-1/2) sigmoid(log_decay + w0))``, ``sigmoid(a + a_bias) * u`` and ``u = k / |k|`` per head."""
+    tokens = proj.shape[0]
+    inner = heads * dim
+    _need(proj.stride(1) == 1, "delta_general_prepare: bad projections")
+    _need(log_decay.dtype == torch.float32 and tuple(log_decay.shape) == (tokens, inner) and log_decay.is_contiguous(), "delta_general_prepare: bad decay input")
+    _need(w0.dtype == torch.float32 and w0.numel() == inner and a_bias.dtype == torch.float32 and a_bias.numel() == inner, "delta_general_prepare: bad constants")
+    _need(len(outs) == 6 and all(o.dtype == torch.float32 and tuple(o.shape) == (tokens, inner) and o.is_contiguous() for o in outs), "delta_general_prepare: bad outputs")
+    ctx.lib.call(
+        "b200_delta_general_prepare", ptr(proj), c_int(proj.stride(0)), *(c_int(o) for o in offsets), ptr(log_decay), ptr(w0), ptr(a_bias),
+        c_int(tokens), c_int(heads), c_int(dim), *(ptr(o) for o in outs), c_int(dtype_code(proj.dtype)), ctx.stream,
+    )
+
+
+def delta_general_recurrence(
+    ctx: StepContext, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, au: torch.Tensor, u: torch.Tensor,
+    state: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int,
+) -> torch.Tensor:
+    """``S <- diag(w) S - au (u^T S) + k v^T``, ``o = S^T r`` per head and token, each request from its slot of ``state``."""
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dk, dv) and state.is_contiguous(), "delta_general_recurrence: the state is float32 [slots, heads, dk, dv]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (r.shape[0], heads * dv) and out.is_contiguous(), "delta_general_recurrence: bad output")
+    ctx.lib.call(
+        "b200_delta_general_recurrence", ptr(r), ptr(k), ptr(v), ptr(w), ptr(au), ptr(u), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len),
+        ptr(ctx.seq_slot), c_int(ctx.num_seqs), c_int(heads), c_int(dk), c_int(dv), ptr(state), ptr(out), ctx.stream,
+    )
+    return out
+
+
+def conv_norm_rope_write(
+    ctx: StepContext, cache: CacheView, conv_state: torch.Tensor, proj: torch.Tensor, bias: torch.Tensor | None, taps: torch.Tensor,
+    q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor | None, rot_dims: int, q_out: torch.Tensor,
+    q_heads: int, kv_heads: int, dim: int, vdim: int, row_dim: int,
+) -> torch.Tensor:
+    """Per token of ``proj`` (rows ``[q | k | v | ...]``): bias, the short convolution over time (continuing each
+    request's slot of ``conv_state``, which is then moved on), one RMS norm over all of q and one over all of k,
+    rotation of the first ``rot_dims`` dims of every head in neighbouring pairs, queries to ``q_out`` and keys
+    and values to the token's page, all in rows of ``row_dim`` numbers padded with zeros."""
+    tokens, ld = proj.shape
+    channels = (q_heads + kv_heads) * dim + kv_heads * vdim
+    _need(proj.is_contiguous() and cache.keys.dtype == proj.dtype and cache.values is not None, "conv_norm_rope_write: bad operands")
+    _need(tuple(q_out.shape) == (tokens, q_heads * row_dim) and q_out.is_contiguous() and q_out.dtype == proj.dtype, "conv_norm_rope_write: bad q_out")
+    _need(tuple(cache.keys.shape[1:]) == (kv_heads, cache.page_size, row_dim), "conv_norm_rope_write: the cache rows differ from the padded head size")
+    _need(taps.dtype == torch.float32 and taps.shape[0] == channels and taps.is_contiguous(), "conv_norm_rope_write: taps are float32 [channels, taps]")
+    _need(conv_state.dtype == proj.dtype and tuple(conv_state.shape[1:]) == (taps.shape[1] - 1, channels), "conv_norm_rope_write: bad convolution state")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == channels), "conv_norm_rope_write: bad bias")
+    _need(q_weight.dtype == torch.float32 and q_weight.numel() == q_heads * dim and k_weight.dtype == torch.float32 and k_weight.numel() == kv_heads * dim, "conv_norm_rope_write: bad norm weights")
+    _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2), "conv_norm_rope_write: bad frequency table")
+    ctx.lib.call(
+        "b200_conv_norm_rope_write", ptr(proj), c_int(ld), ptr(bias), ptr(taps), c_int(taps.shape[1]), ptr(conv_state), ptr(q_weight),
+        ptr(k_weight), c_float(eps), ptr(inv_freq if rot_dims else None), c_int(rot_dims), ptr(ctx.positions), ptr(ctx.token_seq),
+        ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_slot), ptr(ctx.seq_kv_len), ptr(cache.block_table), c_int(cache.max_pages),
+        c_int(cache.num_pages), ptr(cache.keys), ptr(cache.values), ptr(q_out), c_int(tokens), c_int(ctx.num_seqs), c_int(q_heads),
+        c_int(kv_heads), c_int(dim), c_int(vdim), c_int(row_dim), c_int(cache.page_size), c_int(1 if cache.writes else 0),
+        c_int(dtype_code(proj.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    if taps.shape[1] > 1:
+        ctx.lib.calls += 1  # the slot update is a launch of its own
+    return q_out
+
+
+def mix_heads_gate(
+    ctx: StepContext, attn: torch.Tensor, mix: torch.Tensor, gate: torch.Tensor | None, heads: int, kv_heads: int, vdim: int, row_dim: int,
+    out: torch.Tensor,
+) -> torch.Tensor:
+    """``out[t, h] = sigmoid(gate[t, h]) * sum_g mix[h, g] * attn[c(h), t, g, :vdim]``; ``attn`` is ``[kv_heads, tokens,
+    heads * row_dim]`` (plane ``c``: every head's weights applied to the values of kv head ``c``)."""
+    tokens = out.shape[0]
+    _need(tuple(attn.shape) == (kv_heads, tokens, heads * row_dim) and attn.is_contiguous() and tuple(out.shape) == (tokens, heads * vdim) and out.is_contiguous() and out.dtype == attn.dtype, "mix_heads_gate: bad operands")
+    _need(mix.dtype == torch.float32 and tuple(mix.shape) == (heads, heads) and mix.is_contiguous(), "mix_heads_gate: the mix is float32 [heads, heads]")
+    _need(gate is None or (gate.stride(1) == 1 and gate.shape[1] == heads * vdim and gate.dtype == attn.dtype), "mix_heads_gate: bad gate")
+    ctx.lib.call(
+        "b200_mix_heads_gate", ptr(attn), ptr(mix), ptr(gate), c_int(gate.stride(0) if gate is not None else 0), c_int(tokens), c_int(heads),
+        c_int(kv_heads), c_int(vdim), c_int(row_dim), ptr(out), c_int(dtype_code(attn.dtype)), ctx.stream,
+    )
+    return out
+
+
+def pair_norm_add(ctx: StepContext, x_in: torch.Tensor, pair: BranchPair, weight: torch.Tensor, eps: float, x_out: torch.Tensor,
+                  cast: torch.Tensor | None = None) -> None:
+    """``x_out = x_in + weight * y / rms(y)`` with ``y`` the combination of the pair (see :class:`BranchPair`)."""
+    rows, hidden = x_in.shape
+    _need(x_in.dtype == torch.float32 and x_out.dtype == torch.float32 and x_in.is_contiguous() and x_out.is_contiguous(), "pair_norm_add: the stream is contiguous float32")
+    for t in (pair.a, pair.b):
+        _need(tuple(t.shape) == (rows, hidden) and t.is_contiguous() and t.dtype == pair.a.dtype, "pair_norm_add: bad branch outputs")
+    for w in (pair.wa, pair.wb, weight):
+        _need(w.dtype == torch.float32 and w.numel() == hidden, "pair_norm_add: weights are float32 [hidden]")
+    _need(cast is None or (cast.dtype == pair.a.dtype and cast.shape == x_in.shape), "pair_norm_add: bad cast buffer")
+    ctx.lib.call(
+        "b200_pair_norm_add", ptr(x_in), ptr(pair.a), ptr(pair.b), ptr(pair.wa), ptr(pair.wb), ptr(weight), c_int(rows), c_int(hidden),
+        c_float(pair.eps), c_float(eps), ptr(x_out), ptr(cast), c_int(dtype_code(pair.a.dtype)), ctx.stream,
+    )
+
+
+def embedding_bigram(
+    ctx: StepContext, table: torch.Tensor, pairs: torch.Tensor, last_token: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int,
+    out: torch.Tensor, cast: torch.Tensor | None,
+) -> torch.Tensor:
+    """``out[t] = table[token] + pairs[(previous * mul_prev + token * mul_cur) mod buckets]`` (row ``buckets`` for a
+    request's first token) in 32-bit; ``last_token`` ``[slots, 1]`` int32 carries each request's last token."""
+    vocab, hidden = table.shape
+    _need(tuple(out.shape) == (ctx.num_tokens, hidden) and out.dtype == torch.float32, "embedding_bigram: bad output")
+    _need(tuple(pairs.shape) == (buckets + 1, hidden) and pairs.dtype == table.dtype and pairs.is_contiguous(), "embedding_bigram: the pair table is [buckets + 1, hidden]")
+    _need(last_token.dtype == torch.int32 and last_token.is_contiguous(), "embedding_bigram: the slots hold int32")
+    _need(cast is None or (cast.dtype == table.dtype and cast.shape == out.shape), "embedding_bigram: bad cast buffer")
+    ctx.lib.call(
+        "b200_embedding_bigram", ptr(table), ptr(pairs), ptr(ctx.token_ids), ptr(ctx.positions), ptr(ctx.token_seq), ptr(ctx.seq_q_start),
+        ptr(ctx.seq_q_len), ptr(ctx.seq_slot), ptr(last_token), c_int(buckets), c_int64(mul_prev), c_int64(mul_cur), ptr(out), ptr(cast),
+        c_int(ctx.num_tokens), c_int(ctx.num_seqs), c_int(hidden), c_int(vocab), c_int(dtype_code(table.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    ctx.lib.calls += 1  # the slot update is a launch of its own
     return out

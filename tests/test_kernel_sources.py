@@ -23,6 +23,8 @@ BEFORE_THE_CHAIN = {
     "scale", "mix", "coefficients", "norm_weight", "sink", "taps_w", "a_log", "dt_bias",
     # stream weights of the hyper-connections, blend factors, decay offset and bonus of the recurrent mixer with a bonus
     "mix_w", "out_w", "in_w", "mu", "w0", "u",
+    # the step's per-request metadata; norm weights over all heads, weights of a pair of mixers, the pair table
+    "seq_q_start", "seq_q_len", "seq_slot", "a_bias", "q_weight", "k_weight", "wa", "wb", "pairs",
 }
 
 
