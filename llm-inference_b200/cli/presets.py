@@ -39,7 +39,27 @@ def _tunadra(width, vocab, blocks, heads, kv_heads, experts, top, ff):
     }
 
 
+def _lerorax(width, vocab, blocks, heads, kv_heads, ff, shared=False):
+    """``blocks`` pairs of (minGRU layer, attention beside a delta rule); with ``shared`` a second run of pairs
+    uses the first run's tensors."""
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    recurrent = {"type": "mingru", "mlp": mlp, "mixer": {"width": width * 3 // 2}}
+    rot = {"base": 500000.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    pair = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125, "rot": rot},
+        "right": {"heads": width // 64, "dim": 64, "decay_rank": 32}}}
+    layers = [recurrent, pair] * blocks
+    if shared:
+        layers = layers + [dict(layer, weights_of=index) for index, layer in enumerate(layers)]
+    return {
+        "architecture": "Lerorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+        "embedding": {"bigram": {"buckets": 4093, "mul_prev": 8191, "mul_cur": 31}}, "layers": layers,
+    }
+
+
 PRESETS = {
+    "lerorax-small": _lerorax(512, 8192, 2, 8, 2, 1024, shared=True),
+    "lerorax-1b": _lerorax(2048, 32768, 6, 32, 4, 5632),
     "tunadra-small": _tunadra(512, 8192, 3, 8, 2, 16, 2, 256),
     "tiny-a": _qwen2(2, 64, 4, 2, 176, 256, True, 128, rope_theta=10000.0),
     "tiny-b": _qwen2(3, 96, 3, 1, 272, 311, False, 256, rms_norm_eps=1e-5, use_sliding_window=True,

@@ -57,6 +57,7 @@ struct FlashParams {
   int window;
   int splits;
   int cluster_merge;  // the splits of a (request, kv head) are one thread-block cluster and merge on chip
+  int value_head;     // >= 0: every query head's weights meet the values of this kv head instead of its own
   float scale_log2;
 };
 
@@ -118,6 +119,8 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
   const int chunk = threadIdx.x % kChunks;
   const int row0 = threadIdx.x / kChunks;
   const int page_size = p.page_mask + 1;
+  // Values of another kv head lie a fixed distance from the keys' head within the same page.
+  const int64_t v_shift = p.value_head >= 0 ? static_cast<int64_t>(p.value_head - kv_head) * page_size * HEAD_DIM : 0;
   if (page_size >= kTileKeys) {
     // The whole tile lies in one page (tiles start at multiples of 64 and the page size is a
     // power of two): one table entry, then a fixed stride from row to row.
@@ -135,7 +138,7 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
       const bool valid = page_ok && key >= lo && key <= hi;
       const int64_t offset = valid ? base + static_cast<int64_t>(pass) * kRowsPerPass * HEAD_DIM : 0;
       cp_async_16(smem_u32(k_dst + tile_offset<HEAD_DIM>(row, chunk)), p.k_arena + offset, valid);
-      cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset, valid);
+      cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset + (valid ? v_shift : 0), valid);
     }
     return;
   }
@@ -157,7 +160,7 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
                                     (key & p.page_mask)) * HEAD_DIM + chunk * 8
                                  : 0;
     cp_async_16(smem_u32(k_dst + tile_offset<HEAD_DIM>(row, chunk)), p.k_arena + offset, valid);
-    cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset, valid);
+    cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset + (valid ? v_shift : 0), valid);
   }
 }
 
@@ -1041,8 +1044,9 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
                                         int num_seqs, int tokens, int max_q_len, int max_pages,
                                         int num_pages, int q_heads, int kv_heads, int head_dim,
                                         int page_size, int window, float scale, int decode, int splits,
-                                        float* scratch, int* err, cudaStream_t stream) {
+                                        int value_head, float* scratch, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  B200_REQUIRE(value_head < kv_heads, "paged_flash_attention: value head %d of %d", value_head, kv_heads);
   B200_REQUIRE(b200_flash_attention_supported(q_heads, kv_heads, head_dim, page_size, decode),
                "paged_flash_attention: unsupported shape (heads %d/%d, head_dim %d, page %d)", q_heads,
                kv_heads, head_dim, page_size);
@@ -1072,6 +1076,7 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
   p.window = window;
   p.splits = decode ? splits : 1;
   p.cluster_merge = (scratch == nullptr && p.splits > 1) ? 1 : 0;
+  p.value_head = value_head;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;
@@ -1134,6 +1139,7 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   p.window = window;
   p.splits = splits;
   p.cluster_merge = (scratch == nullptr && splits > 1) ? 1 : 0;
+  p.value_head = -1;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;

@@ -30,11 +30,12 @@ def attend(
     value_head: int = -1,
 ) -> None:
     """``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
-    instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head)."""
+    instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head); the
+    mma.sync kernels take it (values by cp.async from the other head's rows of the same page), the TMA
+    and tcgen05 kernels do not."""
     choice = ctx.options.get("attention", "auto")
     tuned = (
         choice != "plain"
-        and value_head < 0
         and q.dtype == torch.bfloat16
         and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=False)
     )
@@ -48,13 +49,13 @@ def attend(
         decode_seqs = 0  # more than 16 query heads per kv head: the prefill form handles one-token runs too
     if decode_seqs:
         reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
-        tma = ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+        tma = value_head < 0 and ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
         splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(decode_seqs, kv_heads, reach, tma, ops.sm_count(ctx))
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
-            first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits,
+            first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head,
         )
-    if ctx.num_seqs > decode_seqs and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+    if ctx.num_seqs > decode_seqs and value_head < 0 and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
         ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
     ):
         ops.paged_prefill_attention_tcgen05(
@@ -66,7 +67,7 @@ def attend(
             raise ops.KernelError("the tcgen05 attention kernel does not take this shape")
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
-            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len,
+            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len, value_head=value_head,
         )
 
 

@@ -454,8 +454,10 @@ def paged_flash_attention(
     decode: bool,
     max_q_len: int,
     splits: int = 1,
+    value_head: int = -1,
 ) -> torch.Tensor:
-    """Tensor-core attention for requests ``first_seq .. first_seq + num_seqs`` of the step."""
+    """Tensor-core attention for requests ``first_seq .. first_seq + num_seqs`` of the step. With ``value_head`` >= 0
+    every query head's weights are applied to the values of that kv head (the cp.async kernel only)."""
     if num_seqs <= 0:
         return out
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "flash attention is bfloat16 only")
@@ -469,7 +471,7 @@ def paged_flash_attention(
     # slow to place. The TMA kernel always goes through scratch unless told otherwise: at
     # batch 1 both forms take 1.10 ms per step (the cp.async kernel 1.15), at batch 2 scratch
     # 1.10 and the cluster 1.12, from batch 4 on the cluster loses.
-    use_tma = decode and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+    use_tma = decode and value_head < 0 and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
     merge = ctx.options.get("attention_merge", "auto")
     if merge == "auto":
         merge = "cluster" if num_seqs * kv_heads <= 4 and not use_tma else "scratch"
@@ -493,7 +495,7 @@ def paged_flash_attention(
         ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs),
         c_int(num_seqs if decode else ctx.num_tokens), c_int(max_q_len), c_int(cache.max_pages), c_int(cache.num_pages),
         c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale),
-        c_int(1 if decode else 0), c_int(splits), ptr(scratch), ptr(ctx.err), ctx.stream,
+        c_int(1 if decode else 0), c_int(splits), c_int(value_head), ptr(scratch), ptr(ctx.err), ctx.stream,
     )
     if scratch is not None:
         ctx.lib.calls += 1  # the merge kernel is a launch of its own

@@ -159,7 +159,7 @@ class Replay:
                 group.arena.fill_(float("nan"))
             for arrays in self.cache.states.values():
                 for array in arrays:
-                    array.fill_(float("nan"))
+                    array.fill_(float("nan") if array.dtype.is_floating_point else -7)
         self.runner = ModelRunner(self.model, self.cache, max_batch_tokens=pool_tokens, options={})
         self.ids: dict[str, int] = {}
         self.next_id = 1

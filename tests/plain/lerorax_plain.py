@@ -238,3 +238,20 @@ class PlainLerorax:
         state["position"] += n
         rows = x if want is None else x[list(want)]
         return norm_around_zero(rows, w["final.norm"], self.eps) @ w["head"].T
+
+
+def forward(config: dict, weights: dict, tokens, layer_outputs=None) -> np.ndarray:
+    """Logits ``[len(tokens), vocab]`` of one whole sequence."""
+    model = PlainLerorax(config, weights)
+    return model.forward(tokens, model.new_state(), layer_outputs=layer_outputs)
+
+
+def greedy(config: dict, weights: dict, prompt, count: int) -> list[int]:
+    model = PlainLerorax(config, weights)
+    state = model.new_state()
+    row = model.forward(prompt, state)[-1]
+    out = []
+    for _ in range(count):
+        out.append(int(np.argmax(row)))
+        row = model.forward([out[-1]], state)[-1]
+    return out
