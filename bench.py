@@ -312,7 +312,30 @@ def tunadra_shape(width: int) -> dict:
     }
 
 
-DESIGN_SHAPES = {"gunedra": gunedra_shape, "tunadra": tunadra_shape}
+def lerorax_shape(width: int) -> dict:
+    """Layer sizes in the proportions of a real model of this design: attention heads of 128 sharing key/value
+    heads as the Qwen2 shape does, four taps, half of each head rotated; beside it a delta rule with heads of
+    64 x 64 over the whole width; a minGRU layer one and a half times as wide as the model; the dense
+    feed-forward of the Qwen2 shape of this width."""
+    heads, ff = DESIGN_SIZES[width]
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    pair = {
+        "type": "parallel", "mlp": mlp,
+        "mixer": {
+            "left": {"heads": heads, "kv_heads": max(1, heads // 6), "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+                     "rot": {"base": 5e5, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+            "right": {"heads": width // 64, "dim": 64, "decay_rank": 64},
+        },
+    }
+    recurrent = {"type": "mingru", "mlp": mlp, "mixer": {"width": width * 3 // 2}}
+    return {
+        "architecture": "Lerorax", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
+        "embedding": {"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}}, "layers": [pair, pair, recurrent, pair][:DESIGN_LAYERS],
+    }
+
+
+DESIGN_SHAPES = {"gunedra": gunedra_shape, "tunadra": tunadra_shape, "lerorax": lerorax_shape}
+# The design each is put beside: the Qwen2 shape of equal width, or (--beside) another design's shape of equal width.
 
 
 def qwen2_shape(width: int) -> dict:
@@ -346,7 +369,9 @@ def compare_designs(args) -> int:
     batch = args.batch
     results = {}
     for width in [int(w) for w in args.design_sizes.split(",")]:
-        for design, raw in ((args.design, DESIGN_SHAPES[args.design](width)), ("qwen2", qwen2_shape(width))):
+        beside = args.beside or ("gunedra" if args.design == "lerorax" else "qwen2")
+        other = qwen2_shape(width) if beside == "qwen2" else DESIGN_SHAPES[beside](width)
+        for design, raw in ((args.design, DESIGN_SHAPES[args.design](width)), (beside, other)):
             _, config = parse_config(raw)
             model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             engine = Engine(model=model, max_num_sequences=max(batch, 8), max_model_length=CONTEXT, num_pages=(batch + 2) * CONTEXT // PAGE,
@@ -484,7 +509,10 @@ def main() -> int:
                         help="instead of the headline run: prefill and decode of another design (--design) beside the Qwen2 shape of "
                         "equal width, feed-forward and head count, at a few layer sizes, with each kernel's time")
     parser.add_argument("--design-sizes", default="1536,3584", help="widths for --designs (1536, 3584 or 5120)")
-    parser.add_argument("--design", choices=["gunedra", "tunadra"], default="gunedra", help="which design --designs puts beside the Qwen2 shape")
+    parser.add_argument("--design", choices=["gunedra", "tunadra", "lerorax"], default="gunedra", help="which design --designs puts beside the Qwen2 shape")
+    parser.add_argument("--beside", choices=["qwen2", "gunedra", "tunadra"], default=None,
+                        help="--designs: the shape of equal width to put the design beside (default: qwen2; for lerorax gunedra, the "
+                        "closest design: blocks that norm their branches' outputs, a delta rule, short convolutions, a dense feed-forward)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

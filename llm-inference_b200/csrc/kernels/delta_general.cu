@@ -202,7 +202,7 @@ B200_API int b200_delta_general_prepare(const void* proj, int ld, int r_at, int 
 
 B200_API int b200_delta_general_recurrence(const float* r, const float* k, const float* v, const float* w, const float* au,
                                            const float* u, const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int seqs,
-                                           int heads, int dk, int dv, float* state, float* out, cudaStream_t stream) {
+                                           int max_q_len, int heads, int dk, int dv, float* state, float* out, cudaStream_t stream) {
   if (seqs == 0) return 0;
   B200_REQUIRE(seqs > 0 && heads > 0 && heads <= 65535 && dk > 0 && dv > 0, "delta_general_recurrence: bad sizes");
   B200_REQUIRE(dk <= 1024, "delta_general_recurrence: %d key channels per head, at most 1024", dk);
@@ -219,10 +219,15 @@ B200_API int b200_delta_general_recurrence(const float* r, const float* k, const
   const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const int vec = dk % 4 == 0 && dv % 4 == 0 && aligned(r) && aligned(k) && aligned(v) && aligned(w) && aligned(au) && aligned(u) ? 1 : 0;
   B200_REQUIRE(smem <= 200 * 1024, "delta_general_recurrence: the staged tokens do not fit shared memory");
+  // A step with prompt portions launches the ordinary way, after the kernel in front has left the SMs. Made resident
+  // early, the few blocks of this kernel are packed onto the few SMs the predecessor's last wave leaves free, several
+  // to an SM, and walk their tokens there to the end: measured on a B200, 2,048 tokens of 24 heads of 64 x 64 took
+  // 1.8 ms that way and 0.63 ms spread one block to an SM. Steps of single tokens keep the early start.
+  const bool ordered = max_q_len > kStage;
   auto launch = [&](auto kernel) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    launch_kernel(kernel, grid, dim3(kRecurrenceThreads), smem, stream, r, k, v, w, au, u, seq_q_start, seq_q_len, seq_slot, heads, dk, dv,
-                  vec, state, out);
+    launch_kernel_as(ordered, kernel, grid, dim3(kRecurrenceThreads), smem, stream, r, k, v, w, au, u, seq_q_start, seq_q_len, seq_slot, heads,
+                     dk, dv, vec, state, out);
   };
   if (per == 32) launch(delta_general_recurrence_kernel<32, 32>);
   else if (per == 16) launch(delta_general_recurrence_kernel<16, 32>);

@@ -106,7 +106,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_clamped_glu": [c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "b200_mingru": [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 4 + [c_void_p] * 3 + [c_int, c_void_p],
     "b200_delta_general_prepare": [c_void_p] + [c_int] * 5 + [c_void_p] * 3 + [c_int] * 3 + [c_void_p] * 6 + [c_int, c_void_p],
-    "b200_delta_general_recurrence": [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 3,
+    "b200_delta_general_recurrence": [c_void_p] * 9 + [c_int] * 5 + [c_void_p] * 3,
     "b200_conv_norm_rope_write": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int]
                                  + [c_void_p] * 7 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 10 + [c_void_p, c_void_p],
     "b200_mix_heads_gate": [c_void_p] * 3 + [c_int] * 6 + [c_void_p, c_int, c_void_p],

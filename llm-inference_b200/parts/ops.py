@@ -1134,7 +1134,7 @@ def delta_general_recurrence(
     _need(out.dtype == torch.float32 and tuple(out.shape) == (r.shape[0], heads * dv) and out.is_contiguous(), "delta_general_recurrence: bad output")
     ctx.lib.call(
         "b200_delta_general_recurrence", ptr(r), ptr(k), ptr(v), ptr(w), ptr(au), ptr(u), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len),
-        ptr(ctx.seq_slot), c_int(ctx.num_seqs), c_int(heads), c_int(dk), c_int(dv), ptr(state), ptr(out), ctx.stream,
+        ptr(ctx.seq_slot), c_int(ctx.num_seqs), c_int(max(ctx.max_q_len, 1)), c_int(heads), c_int(dk), c_int(dv), ptr(state), ptr(out), ctx.stream,
     )
     return out
 
