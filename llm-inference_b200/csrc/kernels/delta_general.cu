@@ -7,7 +7,7 @@
 // low-rank projection, a = sigmoid(pa + a_bias) the share removed per key channel. Everything the
 // recurrence reads is 32-bit.
 //
-// Kernels: `delta_general_prepare` (one block per token: r, k, v as 32-bit, w, a (.) u and u),
+// Kernels: `delta_general_prepare` (one warp per token and head: r, k, v as 32-bit, w, a (.) u and u),
 // `delta_general_recurrence` (the columns of S are independent: column c follows
 // s <- w (.) s - (a (.) u) (u . s) + k v_c, so a thread group owns a column and walks the request's tokens).
 #include "common.cuh"
@@ -28,7 +28,7 @@ __global__ void delta_general_prepare_kernel(const T* proj, int ld, int r_at, in
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const T* row = proj + static_cast<int64_t>(t) * ld;
   const int64_t base = static_cast<int64_t>(t) * heads * dim;
-  for (int head = warp; head < heads; head += warps) {
+  for (int head = blockIdx.y * warps + warp; head < heads; head += gridDim.y * warps) {
     float ss = 0.f;
     for (int i = lane; i < dim; i += 32) {
       const float kv = to_f32<T>(row[k_at + head * dim + i]);
@@ -134,7 +134,7 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
     const float* su = sa + kStage * padded;
     const float* sv = su + kStage * padded;
     const int count = min(kStage, len - t0);
-    for (int j = 0; j < count; ++j) {
+    auto token = [&](int j) {
       const float* rj = sr + j * padded + part;
       const float* kj = sk + j * padded + part;
       const float* wj = sw + j * padded + part;
@@ -163,6 +163,12 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
 #pragma unroll
       for (int o = lanes_per_col >> 1; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
       if (live && part == 0) out[(static_cast<int64_t>(start) + t0 + j) * heads * dv + head * dv + col] = rs;
+    };
+    if (count == kStage) {  // a full stage is unrolled: one token's read-out overlaps the next token's update
+#pragma unroll
+      for (int j = 0; j < kStage; ++j) token(j);
+    } else {
+      for (int j = 0; j < count; ++j) token(j);
     }
     __syncthreads();
   }
@@ -187,11 +193,12 @@ B200_API int b200_delta_general_prepare(const void* proj, int ld, int r_at, int 
                    a_at + inner <= ld,
                "delta_general_prepare: rows of %d numbers do not hold the projections", ld);
   const int threads = 128;
+  const dim3 grid(tokens, static_cast<unsigned>(min((heads + 3) / 4, 65535)));  // four warps, a head each
   if (dtype == DTYPE_F32) {
-    launch_kernel(delta_general_prepare_kernel<float>, dim3(tokens), dim3(threads), 0, stream, static_cast<const float*>(proj), ld, r_at,
+    launch_kernel(delta_general_prepare_kernel<float>, grid, dim3(threads), 0, stream, static_cast<const float*>(proj), ld, r_at,
                   k_at, v_at, a_at, lw, w0, a_bias, heads, dim, r_out, k_out, v_out, w_out, au_out, u_out);
   } else if (dtype == DTYPE_BF16) {
-    launch_kernel(delta_general_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+    launch_kernel(delta_general_prepare_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
                   static_cast<const __nv_bfloat16*>(proj), ld, r_at, k_at, v_at, a_at, lw, w0, a_bias, heads, dim, r_out, k_out, v_out,
                   w_out, au_out, u_out);
   } else {

@@ -151,6 +151,7 @@ ATTENTION_SIZES = [
     dict(heads=4, kv_heads=2, dim=64, vdim=64, conv=5, scale=0.11, rot=(32, 5e5), scaling=(8.0, 1.0, 4.0, 256)),
     dict(heads=6, kv_heads=3, dim=64, vdim=48, conv=2, scale=0.1, rot=(64, 300.0), scaling=(4.0, 1.0, 4.0, 64)),
     dict(heads=2, kv_heads=1, dim=128, vdim=128, conv=3, scale=0.06, rot=(16, 1e3)),
+    dict(heads=2, kv_heads=1, dim=10, vdim=5, conv=2, scale=0.4, rot=(4, 1e3)),  # an odd size: numbers are loaded one by one
 ]
 
 
