@@ -185,8 +185,11 @@ def bench_gemm(args) -> dict:
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * m * n * k / us / 1e6}
 
 
-def bench_attention(args, decode: bool) -> dict:
-    from ..parts import attention_dispatch
+def bench_attention(args, decode: bool, mixed: bool = False) -> dict:
+    """``mixed``: attention whose softmax weights are mixed over heads (parts/mixed_attention.py): one pass per kv
+    head, every query head's weights applied to that head's values, then the kernel that mixes and gates. Its
+    flops count what the passes execute (``kv_heads`` times the scores and the weighted sums of all query heads)."""
+    from ..parts import attention_dispatch, ops
     from ..parts.context import CacheView
 
     q_heads, kv_heads, dim, page = args.q_heads, args.kv_heads, args.head_dim, args.page
@@ -221,14 +224,26 @@ def bench_attention(args, decode: bool) -> dict:
         keys = torch.randn(num_pages, kv_heads, page, dim, device="cuda").to(torch.bfloat16)
         values = torch.randn_like(keys)
         view = CacheView(0, True, keys, values, table, num_pages, tables.shape[1], page, args.window)
+        if mixed:
+            planes = torch.empty(kv_heads, len(positions), q_heads * dim, device="cuda", dtype=torch.bfloat16)
+            talk = torch.randn(q_heads, q_heads, device="cuda")
+            gate = torch.randn_like(q)
+
+            def passes(view=view, planes=planes):
+                for c in range(kv_heads):
+                    attention_dispatch.attend(ctx, view, q, planes[c], q_heads, kv_heads, dim, dim**-0.5, value_head=c)
+                ops.mix_heads_gate(ctx, planes, talk, gate, q_heads, kv_heads, dim, dim, out)
+
+            fns.append(passes)
+            continue
         fns.append(lambda view=view: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5))
     # --rotate: back to back inside a CUDA graph, so that neither the host's launch cost nor
     # the idle gap before a lone launch enters (with one arena the cache stays in L2, as it
     # does in a small model's step, where the layer's keys were written just before).
     us = time_back_to_back(fns, 16 * len(fns)) if args.rotate else time_launches(fns[0], args.iters)
     kv_bytes = sum(lens) * kv_heads * dim * 2 * 2
-    flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs))
-    return {"kernel": "decode_attention" if decode else "prefill_attention", "batch": len(lens), "context": args.context,
+    flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs)) * (kv_heads if mixed else 1)
+    return {"kernel": ("mixed_" if mixed else "") + ("decode_attention" if decode else "prefill_attention"), "batch": len(lens), "context": args.context,
             "tokens": len(positions), "loader": args.loader, "splits": args.splits, "stages": args.stages,
             "layers": args.layers, "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
@@ -328,6 +343,29 @@ def bench_wkv_recurrence(args) -> dict:
     moved = 4.0 * (total * (5 * heads * dim + heads) + 2 * batch * heads * dim * dim)
     return {"kernel": "wkv_recurrence", "batch": batch, "tokens": tokens, "heads": heads, "dim": dim, "us": us,
             "us_per_token": us / tokens, "GBps": moved / us / 1e3, "TFLOPs": 5.0 * total * heads * dim * dim / us / 1e6}
+
+
+def bench_delta_general_recurrence(args) -> dict:
+    """The generalized delta rule's recurrence (parts/delta_rule.py, ``general_delta``) over ``--batch`` requests of
+    ``--tokens`` tokens each: ``--q-heads`` heads with states of ``--head-dim`` x ``--head-dim``. Flops: per token and head
+    three products over the state (the unit key's dot; decay, removal and update; read-out)."""
+    from ..parts import ops
+
+    heads, dim, batch, tokens = args.q_heads, args.head_dim, args.batch, args.tokens
+    runs, starts = [tokens] * batch, [0] * batch
+    ctx = make_ctx([p for r in runs for p in range(r)], [i for i, r in enumerate(runs) for _ in range(r)], starts, runs)
+    ctx.seq_slot = torch.arange(batch, dtype=torch.int32, device="cuda")
+    total = batch * tokens
+    r, k, v = (torch.randn(total, heads * dim, device="cuda") for _ in range(3))
+    u = (k.view(total, heads, dim) / k.view(total, heads, dim).norm(dim=-1, keepdim=True)).reshape(total, heads * dim).contiguous()
+    au = u * torch.rand_like(u)
+    decay = torch.rand(total, heads * dim, device="cuda") * 0.2 + 0.8
+    state = torch.zeros(batch, heads, dim, dim, device="cuda")
+    out = torch.empty(total, heads * dim, device="cuda")
+    us = time_launches(lambda: ops.delta_general_recurrence(ctx, r, k, v, decay, au, u, state, out, heads, dim, dim), args.iters)
+    moved = 4.0 * (total * 7 * heads * dim + 2 * batch * heads * dim * dim)
+    return {"kernel": "delta_general_recurrence", "batch": batch, "tokens": tokens, "heads": heads, "dim": dim, "us": us,
+            "us_per_token": us / tokens, "GBps": moved / us / 1e3, "TFLOPs": 7.0 * total * heads * dim * dim / us / 1e6}
 
 
 def bench_moe_experts(args) -> dict:
@@ -470,7 +508,8 @@ def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident", "timeline",
                                            "latent_decode_attention", "latent_prefill_attention", "delta_recurrence", "wkv_recurrence",
-                                           "moe_experts"])
+                                           "moe_experts", "delta_general_recurrence", "mixed_decode_attention",
+                                           "mixed_prefill_attention"])
     parser.add_argument("--experts", type=int, default=32, help="moe_experts: number of experts")
     parser.add_argument("--top", type=int, default=4, help="moe_experts: experts per token")
     parser.add_argument("--rank", type=int, default=512, help="latent attention: size of the cached latent")
@@ -521,6 +560,10 @@ def main(argv=None) -> int:
         result = bench_wkv_recurrence(args)
     elif args.kernel == "moe_experts":
         result = bench_moe_experts(args)
+    elif args.kernel == "delta_general_recurrence":
+        result = bench_delta_general_recurrence(args)
+    elif args.kernel.startswith("mixed_"):
+        result = bench_attention(args, args.kernel == "mixed_decode_attention", mixed=True)
     else:
         result = bench_attention(args, args.kernel == "decode_attention")
     print(json.dumps(result))
