@@ -44,9 +44,9 @@ def _lerorax(width, vocab, blocks, heads, kv_heads, ff, shared=False):
     uses the first run's tensors."""
     mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
     recurrent = {"type": "mingru", "mlp": mlp, "mixer": {"width": width * 3 // 2}}
-    rot = {"base": 500000.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    rot = {"base": 1e6, "dims": 64, "scaling": {"factor": 16.0, "low": 1.0, "high": 2.0, "original": 4096}}
     pair = {"type": "parallel", "mlp": mlp, "mixer": {
-        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125, "rot": rot},
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 3, "scale": 128 ** -0.5, "rot": rot},
         "right": {"heads": width // 64, "dim": 64, "decay_rank": 32}}}
     layers = [recurrent, pair] * blocks
     if shared:
@@ -58,8 +58,8 @@ def _lerorax(width, vocab, blocks, heads, kv_heads, ff, shared=False):
 
 
 PRESETS = {
-    "lerorax-small": _lerorax(512, 8192, 2, 8, 2, 1024, shared=True),
-    "lerorax-1b": _lerorax(2048, 32768, 6, 32, 4, 5632),
+    "lerorax-small": _lerorax(512, 8192, 2, 4, 2, 1024, shared=True),
+    "lerorax-1b": _lerorax(2048, 32768, 6, 16, 4, 5632),
     "tunadra-small": _tunadra(512, 8192, 3, 8, 2, 16, 2, 256),
     "tiny-a": _qwen2(2, 64, 4, 2, 176, 256, True, 128, rope_theta=10000.0),
     "tiny-b": _qwen2(3, 96, 3, 1, 272, 311, False, 256, rms_norm_eps=1e-5, use_sliding_window=True,

@@ -55,6 +55,7 @@ struct PrefillParams {
   int page_size, page_shift;
   int piece_rows;  // rows per TMA box: min(page_size, 128)
   int window;
+  int value_head;  // >= 0: every block takes its values from this kv head's rows of the pages (keys stay its own)
   float scale_log2;
 };
 
@@ -327,6 +328,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     uint64_t* empty = keys ? k_empty : v_empty;
     unsigned char* ring = keys ? k_ring : v_ring;
     const CUtensorMap* map = keys ? &k_map : &v_map;
+    const int row_head = (keys || p.value_head < 0) ? kv_head : p.value_head;
     for (int it = 0; it < num_tiles; ++it) {
       const int s = it % stages;
       if (it >= stages && !bar_wait(&empty[s], ((it / stages) - 1) & 1)) {
@@ -347,7 +349,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
           continue;
         }
         const int key = (tile_begin + it) * kKeys + piece * p.piece_rows;
-        const int arena_row = (page * p.kv_heads + kv_head) * p.page_size + (key & (p.page_size - 1));
+        const int arena_row = (page * p.kv_heads + row_head) * p.page_size + (key & (p.page_size - 1));
         const int offset = piece * p.piece_rows * 128;
         if (leader) {
           tma_tile(ring + s * kTileBytesA + offset, map, &full[s], 0, arena_row);
@@ -654,13 +656,14 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
                                         const int* block_table, const int* seq_q_start, const int* seq_q_len,
                                         const int* seq_kv_len, int first_seq, int num_seqs, int max_q_len,
                                         int max_kv_len, int max_pages, int num_pages, int q_heads, int kv_heads,
-                                        int head_dim, int page_size, int window, float scale, int* err,
+                                        int head_dim, int page_size, int window, float scale, int value_head, int* err,
                                         cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   B200_REQUIRE(b200_flash_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_size, max_kv_len),
                "flash_prefill_tcgen05: unsupported shape (heads %d/%d, head_dim %d, page %d, %d keys)", q_heads, kv_heads,
                head_dim, page_size, max_kv_len);
   B200_REQUIRE(num_seqs > 0 && num_seqs <= 65535 && max_q_len >= 1, "flash_prefill_tcgen05: bad batch");
+  B200_REQUIRE(value_head < kv_heads, "flash_prefill_tcgen05: value head %d of %d", value_head, kv_heads);
   PrefillParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -681,6 +684,7 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   p.page_shift = shift;
   p.piece_rows = page_size < kKeys ? page_size : kKeys;
   p.window = window;
+  p.value_head = value_head;
   p.scale_log2 = scale * kLog2eA;
   CUtensorMap k_map, v_map;
   const int64_t rows = static_cast<int64_t>(num_pages) * kv_heads * page_size;

@@ -31,8 +31,8 @@ def attend(
 ) -> None:
     """``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
     instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head); the
-    mma.sync kernels take it (values by cp.async from the other head's rows of the same page), the TMA
-    and tcgen05 kernels do not."""
+    mma.sync kernels take it (values by cp.async from the other head's rows of the same page) and so does the
+    tcgen05 prefill kernel (the value boxes' row coordinate names the other head); the TMA decode kernel does not."""
     choice = ctx.options.get("attention", "auto")
     tuned = (
         choice != "plain"
@@ -55,12 +55,12 @@ def attend(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head,
         )
-    if ctx.num_seqs > decode_seqs and value_head < 0 and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+    if ctx.num_seqs > decode_seqs and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
         ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
     ):
         ops.paged_prefill_attention_tcgen05(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
-            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len,
+            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len, value_head=value_head,
         )
     elif ctx.num_seqs > decode_seqs:
         if choice == "tcgen05":

@@ -519,8 +519,10 @@ def paged_prefill_attention_tcgen05(
     first_seq: int,
     num_seqs: int,
     max_q_len: int,
+    value_head: int = -1,
 ) -> torch.Tensor:
-    """Prompt-portion attention on tcgen05 / TMEM for requests ``first_seq ..`` of the step."""
+    """Prompt-portion attention on tcgen05 / TMEM for requests ``first_seq ..`` of the step. ``value_head`` >= 0:
+    every query head's weights are applied to the values of that kv head."""
     if num_seqs <= 0:
         return out
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "tcgen05 attention is bfloat16 only")
@@ -529,7 +531,7 @@ def paged_prefill_attention_tcgen05(
         "b200_flash_prefill_tcgen05", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
         ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs), c_int(max_q_len),
         c_int(ctx.max_kv_len), c_int(cache.max_pages), c_int(cache.num_pages), c_int(q_heads), c_int(kv_heads),
-        c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale), ptr(ctx.err), ctx.stream,
+        c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale), c_int(value_head), ptr(ctx.err), ctx.stream,
     )
     return out
 

@@ -38,7 +38,7 @@ def config_of(width, vocab, layers, bigram=(61, 31, 5), eps=1e-5) -> dict:
     return out
 
 
-# Three configurations that differ in every size. ALPHA: the pair of mixers first, keys and values of different
+# Four configurations that differ in every size. ALPHA: the pair of mixers first, keys and values of different
 # widths, half of each head rotated with stretched long wavelengths (the three ranges of wavelengths all occur),
 # a layer without a feed-forward, a layer that runs an earlier layer's tensors, a delta rule with other heads than
 # the attention. BETA: the minGRU first, all query heads on one key/value head, a single tap (no convolution
@@ -58,11 +58,17 @@ _BETA = [
 ]
 BETA = config_of(40, 131, _BETA + [same_as(_BETA, 1), same_as(_BETA, 0), dict(same_as(_BETA, 1), weights_of=3)], bigram=None, eps=3e-4)
 _GAMMA = [
-    with_mlp(parallel_layer(heads=4, kv_heads=2, dim=64, vdim=64, conv=5, scale=0.11, rot=(32, 5e5), scaling=(8.0, 1.0, 4.0, 256), right_heads=1, right_dim=30, decay_rank=4), 96),
+    with_mlp(parallel_layer(heads=6, kv_heads=2, dim=64, vdim=64, conv=5, scale=0.11, rot=(48, 2e5), scaling=(6.0, 1.0, 3.0, 256), right_heads=1, right_dim=30, decay_rank=4), 96),
     with_mlp(mingru_layer(200), 64),
 ]
 GAMMA = config_of(64, 113, _GAMMA + [same_as(_GAMMA, 0)], bigram=(7, 1, 1))
-CONFIGS = {"alpha": ALPHA, "beta": BETA, "gamma": GAMMA}
+# DELTA: heads of 128 on two key/value heads (prompt portions take the tcgen05 attention kernel), two taps.
+_DELTA = [
+    with_mlp(mingru_layer(72), 56),
+    with_mlp(parallel_layer(heads=4, kv_heads=2, dim=128, vdim=128, conv=2, scale=0.07, rot=(64, 1e4), right_heads=2, right_dim=16, decay_rank=3), 64),
+]
+DELTA = config_of(56, 101, _DELTA + [same_as(_DELTA, 1)], bigram=(13, 5, 3))
+CONFIGS = {"alpha": ALPHA, "beta": BETA, "gamma": GAMMA, "delta": DELTA}
 
 
 def owner(config: dict, index: int) -> int:

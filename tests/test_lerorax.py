@@ -35,9 +35,11 @@ def on_device(array: np.ndarray) -> torch.Tensor:
 
 
 def poison(cache) -> None:
-    """A slot is cleared when it is handed out and pages are never cleared: a request reads only what it wrote."""
+    """A slot is cleared when it is handed out and pages are never cleared: a request reads only what it wrote
+    (and the arena's last page, which no request holds: block tables are padded with it, it stays zero, and kernels
+    that fetch whole tiles read it under a weight of zero)."""
     for group in cache.groups:
-        group.arena.fill_(float("nan"))
+        group.arena[:, :, :-1].fill_(float("nan"))
     for arrays in cache.states.values():
         for array in arrays:
             array.fill_(-7 if array.dtype == torch.int32 else float("nan"))
@@ -51,7 +53,7 @@ def one_layer(layer: dict, width: int = 48) -> dict:
 
 
 @pytest.mark.parametrize("name", ["float32", "bfloat16"])
-@pytest.mark.parametrize("buckets,mul_prev,mul_cur,hidden", [(61, 31, 5, 48), (1, 3, 2, 40), (509, 100003, 77777, 260), (7, 0, 1, 16)])
+@pytest.mark.parametrize("buckets,mul_prev,mul_cur,hidden", [(61, 31, 5, 48), (1, 3, 2, 40), (521, 100003, 77777, 260), (7, 0, 1, 16)])
 def test_bigram_embedding_keeps_the_token_in_front_across_steps(name, buckets, mul_prev, mul_cur, hidden):
     """Two requests in portions of 1, 2, 5 tokens: the row of the pair table follows from the token in front,
     which for a portion's first token comes from the request's slot; a request's very first token takes the last
@@ -148,10 +150,11 @@ ATTENTION_SIZES = [
     dict(),
     dict(heads=5, kv_heads=1, dim=12, vdim=6, conv=1, scale=0.45, rot=None),
     dict(heads=3, kv_heads=3, dim=8, vdim=20, conv=4, scale=0.5, rot=(8, 1e4)),
-    dict(heads=4, kv_heads=2, dim=64, vdim=64, conv=5, scale=0.11, rot=(32, 5e5), scaling=(8.0, 1.0, 4.0, 256)),
+    dict(heads=6, kv_heads=2, dim=64, vdim=64, conv=5, scale=0.11, rot=(48, 2e5), scaling=(6.0, 1.0, 3.0, 256)),
     dict(heads=6, kv_heads=3, dim=64, vdim=48, conv=2, scale=0.1, rot=(64, 300.0), scaling=(4.0, 1.0, 4.0, 64)),
     dict(heads=2, kv_heads=1, dim=128, vdim=128, conv=3, scale=0.06, rot=(16, 1e3)),
     dict(heads=2, kv_heads=1, dim=10, vdim=5, conv=2, scale=0.4, rot=(4, 1e3)),  # an odd size: numbers are loaded one by one
+    dict(heads=4, kv_heads=2, dim=128, vdim=128, conv=2, scale=0.07, rot=(32, 1e4)),  # heads the tcgen05 prefill kernel takes, values of another kv head
 ]
 
 
@@ -174,7 +177,7 @@ def plain_left(config, w64, rows, state=None):
     return out, state
 
 
-@pytest.mark.parametrize("name", ["float32", "bfloat16", "bfloat16-plain"])
+@pytest.mark.parametrize("name", ["float32", "bfloat16", "bfloat16-plain", "bfloat16-tcgen05"])
 @pytest.mark.parametrize("sizes", ATTENTION_SIZES)
 def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
     """150 tokens over pages of 8 in portions that end before, on and after page borders, beside a second request
@@ -183,8 +186,11 @@ def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
     current token; the last token's own key then points away from its query and its value is minus token 2's): with a
     sharp softmax that one far key carries head 0, and through the mix over heads every head. The result without
     it, without the mix, without the convolution or without the gate is far outside the tolerance. In bfloat16 the
-    tensor-core kernels run (every head here is padded to 64 or 128); "bfloat16-plain" asks for the plain one."""
+    tensor-core kernels run (every head here is padded to 64 or 128); "bfloat16-plain" asks for the plain one,
+    "bfloat16-tcgen05" (heads of 128 over pages of 16) for the tcgen05 kernel in every prompt portion."""
     name, _, kernels = name.partition("-")
+    if kernels == "tcgen05" and sizes.get("dim") != 128:
+        pytest.skip("the tcgen05 prefill kernel takes heads of 128")
     dtype, hidden, total = DTYPES[name], 48, 150
     config = one_layer(with_mlp(parallel_layer(**sizes), None))
     m = config["layers"][0]["mixer"]["left"]
@@ -223,9 +229,9 @@ def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
         assert np.abs(changed(**{"v.conv": now}) - want[10]).max() > bound
     mixer = build_left(m, hidden, 1e-5)
     mixer.load(weights, dtype, torch.device("cuda:0"))  # the convolution's last inputs are kept in the dtype the weights were loaded in
-    runner, cache, _ = context_for({0: mixer.cache_spec()}, dtype, [1])
+    runner, cache, _ = context_for({0: mixer.cache_spec()}, dtype, [1], page_size=16 if kernels == "tcgen05" else 8)
     if name == "bfloat16":
-        runner.options["attention"] = "plain" if kernels else "flash"  # "flash" refuses a step it cannot take
+        runner.options["attention"] = kernels or "flash"  # "flash" and "tcgen05" refuse a step they cannot take
     poison(cache)
     cache.open(10), cache.open(11)
     got = {10: [], 11: []}
@@ -350,7 +356,7 @@ def test_clamped_gated_unit(name, hidden, ff, limit):
 def test_rotation_frequencies_with_stretched_long_wavelengths():
     from llm_inference_b200.parts import PartSpec, build_part
 
-    for dims, base, scaling in [(8, 100.0, (4.0, 1.0, 4.0, 64)), (32, 5e5, (8.0, 1.0, 4.0, 256)), (64, 300.0, (4.0, 2.0, 3.0, 100)), (16, 1e4, None)]:
+    for dims, base, scaling in [(8, 100.0, (4.0, 1.0, 4.0, 64)), (48, 2e5, (6.0, 1.0, 3.0, 256)), (64, 300.0, (4.0, 2.0, 3.0, 100)), (16, 1e4, None)]:
         named = dict(zip(("factor", "low", "high", "original"), scaling)) if scaling else None
         part = build_part("position", PartSpec("rotary", dict(head_dim=64, theta=base, rotary_dims=dims, interleaved=True, scaling=named)))
         want = plain.rotary_frequencies(dims, base, named)
@@ -370,7 +376,7 @@ LENGTHS = [1, 2, 3, 9, 31, 70, 150]
 MEAN = dict(MEAN_TOLERANCE, bfloat16=0.06)
 
 
-@pytest.fixture(scope="module", params=["alpha", "beta", "gamma"])
+@pytest.fixture(scope="module", params=["alpha", "beta", "gamma", "delta"])
 def model_case(request, tmp_path_factory):
     config = CONFIGS[request.param]
     weights = draw_weights(config, seed=17 + len(request.param))

@@ -65,7 +65,7 @@ def test_recipe_reads_every_size_from_the_configuration():
     assert scaling == {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64.0}
     assert alpha.blocks[2].mixer.members[0].position.scaling is None
     gamma = Model(parsed(GAMMA)[0].recipe(parsed(GAMMA)[1]))
-    assert gamma.blocks[0].mixer.members[0].row_dim == 64 and gamma.blocks[0].mixer.members[0].position.rotary_dims == 32
+    assert gamma.blocks[0].mixer.members[0].row_dim == 64 and gamma.blocks[0].mixer.members[0].position.rotary_dims == 48
 
 
 @pytest.mark.parametrize("change,message", [
