@@ -51,9 +51,13 @@ __global__ void delta_general_prepare_kernel(const T* proj, int ld, int r_at, in
 }
 
 // A block owns `cols` columns of one head of one request; a column's dk rows are spread over
-// `lanes_per_col` neighbouring lanes (row r on lane r % lanes_per_col), PER rows per lane in
-// registers. The tokens' r, k, w, a (.) u, u and v arrive kStage at a time by cp.async in a ring of
-// two stages, so the next tokens load while these are worked on.
+// `lanes_per_col` neighbouring lanes, PER neighbouring rows per lane in registers (rows lane * PER ..).
+// A lane reads four neighbouring numbers of each vector with one 16-byte load; in shared memory a lane's
+// rows are followed by four unused numbers, which puts the eight lanes that load together on different
+// banks. (Four rows per lane instead of eight, with twice the lanes per column, was slower: 0.36 against
+// 0.28 us per token for 24 heads of 64 x 64, more blocks than SMs and one more step in both sums over lanes.)
+// The tokens' r, k, w, a (.) u, u and v arrive kStage at a time by cp.async in a ring of two stages,
+// so the next tokens load while these are worked on.
 constexpr int kRecurrenceThreads = 128;
 constexpr int kStage = 8;
 constexpr int kVectors = 5;  // r, k, w, au, u
@@ -77,7 +81,8 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
   const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
   const int tid = threadIdx.x;
   const int part = tid % lanes_per_col, col = col0 + tid / lanes_per_col;
-  constexpr int padded = PER * lanes_per_col;
+  constexpr int lane_span = PER + 4;  // a lane's rows in shared memory, and four numbers nobody reads
+  constexpr int padded = lane_span * lanes_per_col;
   constexpr int per_stage = kStage * (kVectors * padded + cols);
   const int start = seq_q_start[seq], len = seq_q_len[seq];
   const bool live = col < dv;
@@ -92,7 +97,9 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
     const int64_t first = static_cast<int64_t>(start) + t0;
     if (vec) {
       for (int idx = tid * 4; idx < count * padded; idx += kRecurrenceThreads * 4) {
-        const int j = idx / padded, row = idx % padded;
+        const int j = idx / padded, place = idx % padded;
+        if (place % lane_span >= PER) continue;
+        const int row = place / lane_span * PER + place % lane_span;
         const int64_t at = ((first + j) * heads + head) * dk + (row < dk ? row : 0);
 #pragma unroll
         for (int n = 0; n < kVectors; ++n) stage_copy<16>(base + n * kStage * padded + idx, sources[n] + at, row < dk);
@@ -103,7 +110,9 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
       }
     } else {
       for (int idx = tid; idx < count * padded; idx += kRecurrenceThreads) {
-        const int j = idx / padded, row = idx % padded;
+        const int j = idx / padded, place = idx % padded;
+        if (place % lane_span >= PER) continue;
+        const int row = place / lane_span * PER + place % lane_span;
         const int64_t at = ((first + j) * heads + head) * dk + (row < dk ? row : 0);
 #pragma unroll
         for (int n = 0; n < kVectors; ++n) stage_copy<4>(base + n * kStage * padded + idx, sources[n] + at, row < dk);
@@ -117,7 +126,7 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
   float s[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
-    const int row = i * lanes_per_col + part;
+    const int row = part * PER + i;
     s[i] = (live && row < dk) ? s_base[static_cast<int64_t>(row) * dv + col] : 0.f;
   }
   if (len > 0) fetch(0, 0);
@@ -134,35 +143,47 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
     const float* su = sa + kStage * padded;
     const float* sv = su + kStage * padded;
     const int count = min(kStage, len - t0);
+    // The read-out of a token is summed over the lanes together with the next token's u . s: the two sums do not
+    // depend on each other, so their shuffles go out in pairs and the warp waits for half as many.
+    float pending = 0.f;
+    int pending_at = -1;
     auto token = [&](int j) {
-      const float* rj = sr + j * padded + part;
-      const float* kj = sk + j * padded + part;
-      const float* wj = sw + j * padded + part;
-      const float* aj = sa + j * padded + part;
-      const float* uj = su + j * padded + part;
+      const int at = j * padded + part * lane_span;
       const float vc = sv[j * cols + tid / lanes_per_col];
+      float rv[PER], kv[PER], wv[PER], av[PER], uv[PER];
+#pragma unroll
+      for (int i = 0; i < PER; i += 4) {
+        *reinterpret_cast<float4*>(rv + i) = *reinterpret_cast<const float4*>(sr + at + i);
+        *reinterpret_cast<float4*>(kv + i) = *reinterpret_cast<const float4*>(sk + at + i);
+        *reinterpret_cast<float4*>(wv + i) = *reinterpret_cast<const float4*>(sw + at + i);
+        *reinterpret_cast<float4*>(av + i) = *reinterpret_cast<const float4*>(sa + at + i);
+        *reinterpret_cast<float4*>(uv + i) = *reinterpret_cast<const float4*>(su + at + i);
+      }
       // u . s over the old state
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
       for (int i = 0; i < PER; i += 2) {
-        d0 = fmaf(uj[i * lanes_per_col], s[i], d0);
-        d1 = fmaf(uj[(i + 1) * lanes_per_col], s[i + 1], d1);
+        d0 = fmaf(uv[i], s[i], d0);
+        d1 = fmaf(uv[i + 1], s[i + 1], d1);
       }
       float dot = d0 + d1;
 #pragma unroll
-      for (int o = lanes_per_col >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      for (int o = lanes_per_col >> 1; o > 0; o >>= 1) {
+        const float from_dot = __shfl_xor_sync(0xffffffffu, dot, o), from_pending = __shfl_xor_sync(0xffffffffu, pending, o);
+        dot += from_dot;
+        pending += from_pending;
+      }
+      if (live && part == 0 && pending_at >= 0) out[(static_cast<int64_t>(start) + pending_at) * heads * dv + head * dv + col] = pending;
       float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
       for (int i = 0; i < PER; i += 2) {
-        s[i] = fmaf(wj[i * lanes_per_col], s[i], fmaf(kj[i * lanes_per_col], vc, -aj[i * lanes_per_col] * dot));
-        s[i + 1] = fmaf(wj[(i + 1) * lanes_per_col], s[i + 1], fmaf(kj[(i + 1) * lanes_per_col], vc, -aj[(i + 1) * lanes_per_col] * dot));
-        rs0 = fmaf(rj[i * lanes_per_col], s[i], rs0);
-        rs1 = fmaf(rj[(i + 1) * lanes_per_col], s[i + 1], rs1);
+        s[i] = fmaf(wv[i], s[i], fmaf(kv[i], vc, -av[i] * dot));
+        s[i + 1] = fmaf(wv[i + 1], s[i + 1], fmaf(kv[i + 1], vc, -av[i + 1] * dot));
+        rs0 = fmaf(rv[i], s[i], rs0);
+        rs1 = fmaf(rv[i + 1], s[i + 1], rs1);
       }
-      float rs = rs0 + rs1;
-#pragma unroll
-      for (int o = lanes_per_col >> 1; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
-      if (live && part == 0) out[(static_cast<int64_t>(start) + t0 + j) * heads * dv + head * dv + col] = rs;
+      pending = rs0 + rs1;
+      pending_at = t0 + j;
     };
     if (count == kStage) {  // a full stage is unrolled: one token's read-out overlaps the next token's update
 #pragma unroll
@@ -170,12 +191,15 @@ delta_general_recurrence_kernel(const float* r, const float* k, const float* v, 
     } else {
       for (int j = 0; j < count; ++j) token(j);
     }
+#pragma unroll
+    for (int o = lanes_per_col >> 1; o > 0; o >>= 1) pending += __shfl_xor_sync(0xffffffffu, pending, o);
+    if (live && part == 0 && pending_at >= 0) out[(static_cast<int64_t>(start) + pending_at) * heads * dv + head * dv + col] = pending;
     __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
-    const int row = i * lanes_per_col + part;
+    const int row = part * PER + i;
     if (live && row < dk) s_base[static_cast<int64_t>(row) * dv + col] = s[i];
   }
 }
@@ -222,10 +246,10 @@ B200_API int b200_delta_general_recurrence(const float* r, const float* k, const
   const int cols = kRecurrenceThreads / lanes;
   const dim3 grid(seqs, heads, (dv + cols - 1) / cols);
   B200_REQUIRE(grid.z <= 65535, "delta_general_recurrence: too many columns");
-  const size_t smem = sizeof(float) * 2 * (kStage * (kVectors * per * lanes + cols));
+  const size_t smem = sizeof(float) * 2 * (kStage * (kVectors * (per + 4) * lanes + cols));
   const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const int vec = dk % 4 == 0 && dv % 4 == 0 && aligned(r) && aligned(k) && aligned(v) && aligned(w) && aligned(au) && aligned(u) ? 1 : 0;
-  B200_REQUIRE(smem <= 200 * 1024, "delta_general_recurrence: the staged tokens do not fit shared memory");
+  B200_REQUIRE(smem <= 227 * 1024, "delta_general_recurrence: the staged tokens of %d key channels per head do not fit shared memory", dk);
   // A step with prompt portions launches the ordinary way, after the kernel in front has left the SMs. Made resident
   // early, the few blocks of this kernel are packed onto the few SMs the predecessor's last wave leaves free, several
   // to an SM, and walk their tokens there to the end: measured on a B200, 2,048 tokens of 24 heads of 64 x 64 took

@@ -253,7 +253,9 @@ def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
 
 
 DELTA_SIZES = [dict(), dict(right_heads=1, right_dim=6, decay_rank=2), dict(right_heads=2, right_dim=40, decay_rank=3), dict(right_heads=3, right_dim=130, decay_rank=4),
-               dict(right_heads=1, right_dim=300, decay_rank=2), dict(right_heads=4, right_dim=64, decay_rank=16)]
+               dict(right_heads=1, right_dim=300, decay_rank=2), dict(right_heads=4, right_dim=64, decay_rank=16),
+               dict(right_heads=2, right_dim=128, decay_rank=8), dict(right_heads=1, right_dim=256, decay_rank=4),
+               dict(right_heads=2, right_dim=32, decay_rank=4), dict(right_heads=1, right_dim=12, decay_rank=2)]
 
 
 def plain_right(config, w64, rows):
