@@ -230,8 +230,7 @@ def bench_attention(args, decode: bool, mixed: bool = False) -> dict:
             gate = torch.randn_like(q)
 
             def passes(view=view, planes=planes):
-                for c in range(kv_heads):
-                    attention_dispatch.attend(ctx, view, q, planes[c], q_heads, kv_heads, dim, dim**-0.5, value_head=c)
+                attention_dispatch.attend_value_planes(ctx, view, q, planes, q_heads, kv_heads, dim, dim**-0.5)
                 ops.mix_heads_gate(ctx, planes, talk, gate, q_heads, kv_heads, dim, dim, out)
 
             fns.append(passes)

@@ -58,6 +58,8 @@ struct FlashParams {
   int splits;
   int cluster_merge;  // the splits of a (request, kv head) are one thread-block cluster and merge on chip
   int value_head;     // >= 0: every query head's weights meet the values of this kv head instead of its own
+  int plane_tokens;   // > 0 (decoded tokens only): grid.y counts (value head, kv head) pairs, one pass per value head in
+                      // one launch; value head c's results lie c * plane_tokens token rows further in `out` and in scratch
   float scale_log2;
 };
 
@@ -112,7 +114,8 @@ __device__ __forceinline__ int tile_offset(int row, int chunk) {
 // copy would wait a full memory round trip for its page id.
 template <int HEAD_DIM>
 __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v_dst, const int* table,
-                                          const FlashParams& p, int kv_head, int tile_start, int lo, int hi) {
+                                          const FlashParams& p, int kv_head, int value_head, int tile_start, int lo,
+                                          int hi) {
   constexpr int kChunks = HEAD_DIM / 8;
   constexpr int kRowsPerPass = kFlashThreads / kChunks;
   constexpr int kPasses = kTileKeys / kRowsPerPass;
@@ -120,7 +123,7 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
   const int row0 = threadIdx.x / kChunks;
   const int page_size = p.page_mask + 1;
   // Values of another kv head lie a fixed distance from the keys' head within the same page.
-  const int64_t v_shift = p.value_head >= 0 ? static_cast<int64_t>(p.value_head - kv_head) * page_size * HEAD_DIM : 0;
+  const int64_t v_shift = value_head >= 0 ? static_cast<int64_t>(value_head - kv_head) * page_size * HEAD_DIM : 0;
   if (page_size >= kTileKeys) {
     // The whole tile lies in one page (tiles start at multiples of 64 and the page size is a
     // power of two): one table entry, then a fixed stride from row to row.
@@ -173,6 +176,10 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
 // merge kernel, or through the cluster's shared memory. FINISH_ANY decides at run time; the
 // kernels that are compiled for one way carry no code for the others (a block runs this once,
 // from a cold instruction cache).
+// `value_head` of the launcher: one launch runs the pass of every value head (decoded tokens only); `out` is then
+// [kv_heads][tokens, q_heads, head_dim] and scratch holds kv_heads times as many rows.
+constexpr int kEveryValueHead = -2;
+
 enum : int { FINISH_ANY = -1, FINISH_WHOLE = 0, FINISH_PARTIAL = 1, FINISH_CLUSTER = 2 };
 
 template <int HEAD_DIM, int FINISH = FINISH_ANY>
@@ -326,7 +333,12 @@ paged_flash_attention_kernel(const FlashParams p) {
   if (!DECODE) wait_for_predecessor();
   let_successor_start();
   const int seq = p.first_seq + blockIdx.z;
-  const int kv_head = blockIdx.y;
+  int kv_head = blockIdx.y, value_head = p.value_head, plane_shift = 0;
+  if (DECODE && p.plane_tokens > 0) {
+    value_head = blockIdx.y / p.kv_heads;
+    kv_head = blockIdx.y - value_head * p.kv_heads;
+    plane_shift = value_head * p.plane_tokens;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_len = p.seq_q_len[seq];
   const int kv_len = p.seq_kv_len[seq];
@@ -383,7 +395,7 @@ paged_flash_attention_kernel(const FlashParams p) {
   // slot of the ring gets its own commit group, empty if the range is shorter.
   auto fetch = [&](int it) {
     const int slot = it % kRing;
-    load_tile<HEAD_DIM>(k_tiles + slot * kTileBytes, v_tiles + slot * kTileBytes, table, p, kv_head,
+    load_tile<HEAD_DIM>(k_tiles + slot * kTileBytes, v_tiles + slot * kTileBytes, table, p, kv_head, value_head,
                         (tile_begin + it) * kTileKeys, lo, hi);
   };
   int issued = 0;
@@ -547,7 +559,7 @@ paged_flash_attention_kernel(const FlashParams p) {
     return;
   }
 
-  finish_decode_block<HEAD_DIM>(p, smem, o, m0, l0, m1, l1, rows_total, kv_head, q_start, split);
+  finish_decode_block<HEAD_DIM>(p, smem, o, m0, l0, m1, l1, rows_total, kv_head, q_start + plane_shift, split);
 }
 
 // out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M), one block
@@ -943,7 +955,8 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
     configured = true;
   }
   if (decode) {
-    const dim3 grid(p.splits, p.kv_heads, num_seqs);
+    const int planes = p.plane_tokens > 0 ? p.kv_heads : 1;
+    const dim3 grid(p.splits, p.kv_heads * planes, num_seqs);
     if (p.splits > 1 && p.cluster_merge) {
       static bool wide_clusters = false;
       if (p.splits > 8 && !wide_clusters) {
@@ -972,7 +985,7 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
     }
     launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
-      launch_merge<HEAD_DIM>(p.partial_out, p.partial_ml, p.out, tokens * p.q_heads, p.splits, stream);
+      launch_merge<HEAD_DIM>(p.partial_out, p.partial_ml, p.out, planes * tokens * p.q_heads, p.splits, stream);
     }
   } else {
     const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
@@ -1046,7 +1059,10 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
                                         int page_size, int window, float scale, int decode, int splits,
                                         int value_head, float* scratch, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  const bool every_value_head = value_head == kEveryValueHead;
   B200_REQUIRE(value_head < kv_heads, "paged_flash_attention: value head %d of %d", value_head, kv_heads);
+  B200_REQUIRE(!every_value_head || (decode && first_seq == 0 && kv_heads * kv_heads <= 65535),
+               "paged_flash_attention: every value head in one launch is for steps of decoded tokens only");
   B200_REQUIRE(b200_flash_attention_supported(q_heads, kv_heads, head_dim, page_size, decode),
                "paged_flash_attention: unsupported shape (heads %d/%d, head_dim %d, page %d)", q_heads,
                kv_heads, head_dim, page_size);
@@ -1076,11 +1092,13 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
   p.window = window;
   p.splits = decode ? splits : 1;
   p.cluster_merge = (scratch == nullptr && p.splits > 1) ? 1 : 0;
-  p.value_head = value_head;
+  p.value_head = every_value_head ? -1 : value_head;
+  p.plane_tokens = every_value_head ? tokens : 0;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;
-  p.partial_ml = scratch ? scratch + static_cast<int64_t>(tokens) * q_heads * p.splits * head_dim : nullptr;
+  const int64_t planes = every_value_head ? kv_heads : 1;
+  p.partial_ml = scratch ? scratch + planes * tokens * q_heads * p.splits * head_dim : nullptr;
   if (head_dim == 64) return launch_flash<64>(p, num_seqs, decode, max_q_len, tokens, stream);
   return launch_flash<128>(p, num_seqs, decode, max_q_len, tokens, stream);
 }
@@ -1140,6 +1158,7 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   p.splits = splits;
   p.cluster_merge = (scratch == nullptr && splits > 1) ? 1 : 0;
   p.value_head = -1;
+  p.plane_tokens = 0;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;

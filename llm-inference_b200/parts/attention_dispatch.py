@@ -71,6 +71,41 @@ def attend(
         )
 
 
+def attend_value_planes(
+    ctx: StepContext,
+    cache: CacheView,
+    q: torch.Tensor,
+    planes: torch.Tensor,
+    q_heads: int,
+    kv_heads: int,
+    head_dim: int,
+    scale: float,
+) -> None:
+    """``planes[c]`` = every query head's weights applied to the values of kv head ``c``, for every ``c``. A step of
+    decoded tokens only runs all passes as one launch of the split-key kernel (its grid counts pairs of value head and
+    kv head): such steps are bound by launches and by the latency of one pass, not by the keys read. Other steps run
+    one pass per kv head through ``attend``."""
+    choice = ctx.options.get("attention", "auto")
+    decode_only = ctx.num_decode_seqs == ctx.num_seqs and ctx.num_seqs == ctx.num_tokens
+    if (
+        decode_only
+        and kv_heads > 1
+        and choice != "plain"
+        and q.dtype == torch.bfloat16
+        and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=True)
+        and ctx.options.get("value_planes", "auto") != "passes"
+    ):
+        reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
+        splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(ctx.num_seqs, kv_heads * kv_heads, reach, False, ops.sm_count(ctx))
+        ops.paged_flash_attention(
+            ctx, cache, q, planes, q_heads, kv_heads, head_dim, scale,
+            first_seq=0, num_seqs=ctx.num_seqs, decode=True, max_q_len=1, splits=splits, value_head=ops.EVERY_VALUE_HEAD,
+        )
+        return
+    for c in range(kv_heads):
+        attend(ctx, cache, q, planes[c], q_heads, kv_heads, head_dim, scale, value_head=c)
+
+
 def attend_latent(
     ctx: StepContext,
     cache: CacheView,

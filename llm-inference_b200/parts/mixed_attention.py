@@ -93,8 +93,7 @@ class MixedHeadAttention(Part):
         self.position.apply_after_conv_norm(ctx, pages, slots.state[0], proj, self.bias, self.taps_w, self.q_weight, self.k_weight,
                                             self.eps, q, heads, kvh, self.dim, self.vdim, row)
         planes = ctx.buffer("mixed_attn", (kvh, t, heads * row))
-        for c in range(kvh):
-            attention_dispatch.attend(ctx, pages, q, planes[c], heads, kvh, row, self.scale, value_head=c)
+        attention_dispatch.attend_value_planes(ctx, pages, q, planes, heads, kvh, row, self.scale)
         gated = ops.mix_heads_gate(ctx, planes, self.talk, proj[:, self.channels:], heads, kvh, self.vdim, row,
                                    ctx.buffer("attn", (t, heads * self.vdim)))
         return ops.linear(ctx, gated, self.w_o, ctx.buffer(self.out_name, (t, self.hidden_size)))

@@ -407,6 +407,9 @@ def sm_count(ctx: StepContext) -> int:
     return int(ctx.lib.lib.b200_sm_count())
 
 
+EVERY_VALUE_HEAD = -2  # `value_head` of paged_flash_attention: the passes of all kv heads in one launch
+
+
 def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = False, num_sms: int = NUM_SMS) -> int:
     """How many blocks cut each request's keys in a decode step: at least one 64-key tile
     each, and few enough that the merge of their partial results stays cheap. The cp.async
@@ -457,9 +460,16 @@ def paged_flash_attention(
     value_head: int = -1,
 ) -> torch.Tensor:
     """Tensor-core attention for requests ``first_seq .. first_seq + num_seqs`` of the step. With ``value_head`` >= 0
-    every query head's weights are applied to the values of that kv head (the cp.async kernel only)."""
+    every query head's weights are applied to the values of that kv head (the cp.async kernel only). With
+    ``EVERY_VALUE_HEAD`` (a step of decoded tokens only) one launch runs that pass for every kv head and ``out`` is
+    ``[kv_heads, tokens, q_heads * head_dim]``."""
     if num_seqs <= 0:
         return out
+    planes = 1
+    if value_head == EVERY_VALUE_HEAD:
+        _need(decode and num_seqs == ctx.num_tokens, "flash attention: every value head in one launch is for steps of decoded tokens only")
+        _need(out.shape[0] == kv_heads and out.shape[1] == num_seqs, "flash attention: one plane of results per value head")
+        planes = kv_heads
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "flash attention is bfloat16 only")
     _need(q.is_contiguous() and out.is_contiguous(), "flash attention: operands must be contiguous")
     _need(not decode or first_seq == 0, "flash attention: decoded tokens must lead the batch")
@@ -471,12 +481,12 @@ def paged_flash_attention(
     # slow to place. The TMA kernel always goes through scratch unless told otherwise: at
     # batch 1 both forms take 1.10 ms per step (the cp.async kernel 1.15), at batch 2 scratch
     # 1.10 and the cluster 1.12, from batch 4 on the cluster loses.
-    use_tma = decode and value_head < 0 and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+    use_tma = decode and value_head == -1 and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
     merge = ctx.options.get("attention_merge", "auto")
     if merge == "auto":
-        merge = "cluster" if num_seqs * kv_heads <= 4 and not use_tma else "scratch"
+        merge = "cluster" if num_seqs * kv_heads * planes <= 4 and not use_tma else "scratch"
     if decode and splits > 1 and (splits > 16 or merge == "scratch"):
-        scratch = ctx.buffer("attention_partials", (num_seqs * q_heads * splits * (head_dim + 2),), torch.float32, per_token=False)
+        scratch = ctx.buffer("attention_partials", (planes * num_seqs * q_heads * splits * (head_dim + 2),), torch.float32, per_token=False)
     # Keys and values by TMA into per-warp rings where the shape allows; "cp_async" keeps the
     # block-wide cp.async tiles.
     if use_tma:

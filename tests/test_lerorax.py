@@ -177,7 +177,7 @@ def plain_left(config, w64, rows, state=None):
     return out, state
 
 
-@pytest.mark.parametrize("name", ["float32", "bfloat16", "bfloat16-plain", "bfloat16-tcgen05"])
+@pytest.mark.parametrize("name", ["float32", "bfloat16", "bfloat16-plain", "bfloat16-tcgen05", "bfloat16-passes"])
 @pytest.mark.parametrize("sizes", ATTENTION_SIZES)
 def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
     """150 tokens over pages of 8 in portions that end before, on and after page borders, beside a second request
@@ -187,7 +187,9 @@ def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
     sharp softmax that one far key carries head 0, and through the mix over heads every head. The result without
     it, without the mix, without the convolution or without the gate is far outside the tolerance. In bfloat16 the
     tensor-core kernels run (every head here is padded to 64 or 128); "bfloat16-plain" asks for the plain one,
-    "bfloat16-tcgen05" (heads of 128 over pages of 16) for the tcgen05 kernel in every prompt portion."""
+    "bfloat16-tcgen05" (heads of 128 over pages of 16) for the tcgen05 kernel in every prompt portion. Steps of single
+    tokens only (the last five, and those beside the second request's single tokens) run the passes of all kv heads
+    as one launch; "bfloat16-passes" runs them one by one there too."""
     name, _, kernels = name.partition("-")
     if kernels == "tcgen05" and sizes.get("dim") != 128:
         pytest.skip("the tcgen05 prefill kernel takes heads of 128")
@@ -231,7 +233,9 @@ def test_attention_with_mixed_heads_alone_in_portions(name, sizes):
     mixer.load(weights, dtype, torch.device("cuda:0"))  # the convolution's last inputs are kept in the dtype the weights were loaded in
     runner, cache, _ = context_for({0: mixer.cache_spec()}, dtype, [1], page_size=16 if kernels == "tcgen05" else 8)
     if name == "bfloat16":
-        runner.options["attention"] = kernels or "flash"  # "flash" and "tcgen05" refuse a step they cannot take
+        runner.options["attention"] = "flash" if kernels in ("", "passes") else kernels  # "flash" and "tcgen05" refuse a step they cannot take
+        if kernels == "passes":
+            runner.options["value_planes"] = "passes"
     poison(cache)
     cache.open(10), cache.open(11)
     got = {10: [], 11: []}
