@@ -1,5 +1,6 @@
 from .gunedra_config import GunedraConfig
 from .lerorax_config import LeroraxConfig
+from .zetizen_config import ZetizenConfig
 from .model_config import ConfigError, ModelConfig, Qwen2Config, read_config_json
 from .registry import (
     Architecture,
@@ -16,6 +17,7 @@ __all__ = [
     "LeroraxConfig",
     "ModelConfig",
     "Qwen2Config",
+    "ZetizenConfig",
     "parse_config",
     "read_config_json",
     "register_architecture",

@@ -61,6 +61,8 @@ struct FlashParams {
   int plane_tokens;   // > 0 (decoded tokens only): grid.y counts (value head, kv head) pairs, one pass per value head in
                       // one launch; value head c's results lie c * plane_tokens token rows further in `out` and in scratch
   float scale_log2;
+  float scale;       // the shaped form caps and biases the scaled score before it goes to base 2
+  ScoreShape shape;  // soft cap, bias by distance, chunk of visible keys (the SHAPED instantiations only)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -316,7 +318,9 @@ __device__ __forceinline__ void finish_decode_block(const FlashParams& p, unsign
   cluster_sync_all();  // nobody leaves while its shared memory is still being read
 }
 
-template <int HEAD_DIM, bool DECODE>
+// SHAPED: scores pass `shaped_score` (soft cap, bias by distance) and a query sees only the keys of its own chunk of
+// positions; the other instantiations carry none of that code.
+template <int HEAD_DIM, bool DECODE, bool SHAPED = false>
 __global__ void __launch_bounds__(kFlashThreads)
 paged_flash_attention_kernel(const FlashParams p) {
   constexpr int kKSteps = HEAD_DIM / 16;   // k-steps of the score product
@@ -367,6 +371,8 @@ paged_flash_attention_kernel(const FlashParams p) {
     block_last_token = min(q_len - 1, (blockIdx.x * (kWarps * 16) + kWarps * 16 - 1) / p.group);
   }
   int lo = p.window > 0 ? max(0, first_pos + block_first_token - p.window + 1) : 0;
+  const int chunk = SHAPED ? p.shape.chunk : 0;
+  if (SHAPED && chunk > 0) lo = max(lo, (first_pos + block_first_token) / chunk * chunk);  // the block's first row sees furthest back
   int hi = first_pos + block_last_token;  // inclusive
   int tile_begin = lo / kTileKeys, tile_end = hi / kTileKeys + 1;
   if (DECODE && p.splits > 1) {
@@ -384,6 +390,9 @@ paged_flash_attention_kernel(const FlashParams p) {
   const int head1 = kv_head * p.group + (r1 - tok1 * p.group);
   const bool live0 = r0 < rows_total, live1 = r1 < rows_total;
   const int pos0 = first_pos + tok0, pos1 = first_pos + tok1;
+  const int chunk_lo0 = SHAPED && chunk > 0 ? pos0 / chunk * chunk : 0, chunk_lo1 = SHAPED && chunk > 0 ? pos1 / chunk * chunk : 0;
+  const float* bias0 = SHAPED && p.shape.bias ? p.shape.bias + static_cast<int64_t>(head0) * (p.shape.bias_reach + 1) : nullptr;
+  const float* bias1 = SHAPED && p.shape.bias ? p.shape.bias + static_cast<int64_t>(head1) * (p.shape.bias_reach + 1) : nullptr;
 
   float o[kDimTiles][4];
 #pragma unroll
@@ -440,7 +449,7 @@ paged_flash_attention_kernel(const FlashParams p) {
     // Does any element of this tile need masking for this warp's rows?
     const bool tile_needs_mask =
         (tile_start + kTileKeys - 1 > first_pos + min(tok0, q_len - 1)) ||
-        (p.window > 0 && tile_start <= pos1 - p.window) || (tile_start < lo) || !live1;
+        (p.window > 0 && tile_start <= pos1 - p.window) || (tile_start < lo) || !live1 || (SHAPED && chunk > 0);
 
     {
       // A prefill warp takes all 64 keys of the tile for its 16 rows (eight independent score
@@ -473,11 +482,14 @@ paged_flash_attention_kernel(const FlashParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = s[n][e] * p.scale_log2;
+          const int key = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
+          const int pos = e < 2 ? pos0 : pos1;
+          if (SHAPED)
+            v = shaped_score(s[n][e] * p.scale, p.shape, e < 2 ? bias0 : bias1, max(pos - key, 0)) * kLog2e;
           if (tile_needs_mask) {
-            const int key = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
-            const int pos = e < 2 ? pos0 : pos1;
             const bool live = e < 2 ? live0 : live1;
-            const bool visible = live && key <= pos && key >= lo && (p.window == 0 || key > pos - p.window);
+            const bool visible = live && key <= pos && key >= lo && (p.window == 0 || key > pos - p.window) &&
+                                 (!SHAPED || key >= (e < 2 ? chunk_lo0 : chunk_lo1));
             if (!visible) v = -INFINITY;
           }
           s[n][e] = v;
@@ -939,16 +951,16 @@ constexpr size_t flash_smem_bytes(bool decode) {
   return tiles > merge ? tiles : merge;
 }
 
-template <int HEAD_DIM>
+template <int HEAD_DIM, bool SHAPED>
 int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, int tokens,
                  cudaStream_t stream) {
   const size_t smem = flash_smem_bytes<HEAD_DIM>(decode != 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t a = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true>,
+    cudaError_t a = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true, SHAPED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(flash_smem_bytes<HEAD_DIM>(true)));
-    cudaError_t b = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, false>,
+    cudaError_t b = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, false, SHAPED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(flash_smem_bytes<HEAD_DIM>(false)));
     if (a != cudaSuccess || b != cudaSuccess) return b200_fail("flash attention: cannot size shared memory");
@@ -960,7 +972,7 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
     if (p.splits > 1 && p.cluster_merge) {
       static bool wide_clusters = false;
       if (p.splits > 8 && !wide_clusters) {
-        if (cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true>,
+        if (cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true, SHAPED>,
                                  cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
           return b200_fail("flash attention: clusters of %d blocks are not allowed here", p.splits);
         wide_clusters = true;
@@ -979,18 +991,18 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
       attributes[1].val.programmaticStreamSerializationAllowed = 1;
       config.attrs = attributes;
       config.numAttrs = b200_overlap_enabled() ? 2 : 1;
-      const cudaError_t status = cudaLaunchKernelEx(&config, paged_flash_attention_kernel<HEAD_DIM, true>, p);
+      const cudaError_t status = cudaLaunchKernelEx(&config, paged_flash_attention_kernel<HEAD_DIM, true, SHAPED>, p);
       if (status != cudaSuccess) return b200_fail("flash attention: %s", cudaGetErrorString(status));
       return 0;
     }
-    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
+    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true, SHAPED>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
       launch_merge<HEAD_DIM>(p.partial_out, p.partial_ml, p.out, planes * tokens * p.q_heads, p.splits, stream);
     }
   } else {
     const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
     const dim3 grid(row_blocks, p.kv_heads, num_seqs);
-    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, false>, grid, dim3(kFlashThreads), smem, stream, p);
+    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, false, SHAPED>, grid, dim3(kFlashThreads), smem, stream, p);
   }
   return b200_check_launch("paged_flash_attention");
 }
@@ -1057,8 +1069,11 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
                                         int num_seqs, int tokens, int max_q_len, int max_pages,
                                         int num_pages, int q_heads, int kv_heads, int head_dim,
                                         int page_size, int window, float scale, int decode, int splits,
-                                        int value_head, float* scratch, int* err, cudaStream_t stream) {
+                                        int value_head, float softcap, const float* bias, int bias_reach, int chunk,
+                                        float* scratch, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  B200_REQUIRE(softcap >= 0.f && chunk >= 0 && (bias == nullptr || bias_reach >= 0), "paged_flash_attention: bad score shape");
+  const bool shaped = softcap > 0.f || bias != nullptr || chunk > 0;
   const bool every_value_head = value_head == kEveryValueHead;
   B200_REQUIRE(value_head < kv_heads, "paged_flash_attention: value head %d of %d", value_head, kv_heads);
   B200_REQUIRE(!every_value_head || (decode && first_seq == 0 && kv_heads * kv_heads <= 65535),
@@ -1095,12 +1110,18 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
   p.value_head = every_value_head ? -1 : value_head;
   p.plane_tokens = every_value_head ? tokens : 0;
   p.scale_log2 = scale * kLog2e;
+  p.scale = scale;
+  p.shape = ScoreShape{softcap, bias, bias_reach, chunk};
   p.err = err;
   p.partial_out = scratch;
   const int64_t planes = every_value_head ? kv_heads : 1;
   p.partial_ml = scratch ? scratch + planes * tokens * q_heads * p.splits * head_dim : nullptr;
-  if (head_dim == 64) return launch_flash<64>(p, num_seqs, decode, max_q_len, tokens, stream);
-  return launch_flash<128>(p, num_seqs, decode, max_q_len, tokens, stream);
+  if (shaped) {
+    if (head_dim == 64) return launch_flash<64, true>(p, num_seqs, decode, max_q_len, tokens, stream);
+    return launch_flash<128, true>(p, num_seqs, decode, max_q_len, tokens, stream);
+  }
+  if (head_dim == 64) return launch_flash<64, false>(p, num_seqs, decode, max_q_len, tokens, stream);
+  return launch_flash<128, false>(p, num_seqs, decode, max_q_len, tokens, stream);
 }
 
 // Shapes the TMA-fed decode kernel takes: head_dim 128, pages of at least 64 rows (a 64-key
@@ -1160,6 +1181,8 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   p.value_head = -1;
   p.plane_tokens = 0;
   p.scale_log2 = scale * kLog2e;
+  p.scale = scale;
+  p.shape = ScoreShape{0.f, nullptr, 0, 0};
   p.err = err;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<int64_t>(num_seqs) * q_heads * splits * head_dim : nullptr;

@@ -8,6 +8,10 @@
 // (portable.py:173-188); keys are taken 128 at a time with the usual max/sum rescaling, so
 // any context length works. This kernel serves the 32-bit path and every shape the tuned
 // kernels refuse.
+//
+// Beyond the scale a score may be shaped (ScoreShape in common.cuh): soft-capped, s <- cap * tanh(s / cap); given a
+// learned bias by the key's distance, read from a table [q_heads][reach + 1] at min(pos - key, reach) and added after
+// the cap; and restricted to the query's own chunk of positions, keys from floor(pos / chunk) * chunk on.
 #include "common.cuh"
 
 namespace {
@@ -51,7 +55,8 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
                              const int* __restrict__ token_seq,
                              const int* __restrict__ block_table, int max_pages, int num_pages,
                              T* __restrict__ out, int q_heads, int kv_heads, int head_dim,
-                             int page_size, int window, float scale, int value_head, int* __restrict__ err) {
+                             int page_size, int window, float scale, int value_head, const ScoreShape shape,
+                             int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                  // [head_dim]
   float* probs = qs + head_dim;                                    // [kThreads]
@@ -64,7 +69,9 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
   const int kvh = h / (q_heads / kv_heads);
   // With `value_head` >= 0 every query head's weights meet the values of that one head instead of its own.
   const int64_t v_shift = value_head >= 0 ? static_cast<int64_t>(value_head - kvh) * page_size * head_dim : 0;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (shape.chunk > 0) lo = max(lo, pos / shape.chunk * shape.chunk);
+  const float* bias_row = shape.bias ? shape.bias + static_cast<int64_t>(h) * (shape.bias_reach + 1) : nullptr;
   const int* table = block_table + static_cast<int64_t>(seq) * max_pages;
 
   const T* qrow = q + (static_cast<int64_t>(t) * q_heads + h) * head_dim;
@@ -87,7 +94,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_ar
         atomicOr(err, ERRBIT_BAD_PAGE);
       } else {
         off = kv_row_offset(page, kvh, j % page_size, kv_heads, page_size, head_dim);
-        s = dot_row(qs, k_arena + off, head_dim) * scale;
+        s = shaped_score(dot_row(qs, k_arena + off, head_dim) * scale, shape, bias_row, pos - j);
       }
     }
     offsets[tid] = off;
@@ -131,8 +138,11 @@ B200_API int b200_paged_attention_plain(const void* q, const void* k_arena, cons
                                         const int* block_table, int max_pages, int num_pages,
                                         void* out, int tokens, int q_heads, int kv_heads,
                                         int head_dim, int page_size, int window, float scale,
-                                        int value_head, int dtype, int* err, cudaStream_t stream) {
+                                        int value_head, float softcap, const float* bias, int bias_reach, int chunk,
+                                        int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
+  B200_REQUIRE(softcap >= 0.f && chunk >= 0 && (bias == nullptr || bias_reach >= 0), "paged_attention_plain: bad score shape");
+  const ScoreShape shape{softcap, bias, bias_reach, chunk};
   B200_REQUIRE(tokens > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                "paged_attention_plain: %d query heads over %d kv heads", q_heads, kv_heads);
   B200_REQUIRE(head_dim > 0 && head_dim % 8 == 0 && head_dim <= kThreads * kMaxDimsPerThread,
@@ -148,13 +158,13 @@ B200_API int b200_paged_attention_plain(const void* q, const void* k_arena, cons
         static_cast<const float*>(q), static_cast<const float*>(k_arena),
         static_cast<const float*>(v_arena), positions, token_seq, block_table, max_pages,
         num_pages, static_cast<float*>(out), q_heads, kv_heads, head_dim, page_size, window, scale,
-        value_head, err);
+        value_head, shape, err);
   } else if (dtype == DTYPE_BF16) {
     paged_attention_plain_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_arena),
         static_cast<const __nv_bfloat16*>(v_arena), positions, token_seq, block_table, max_pages,
         num_pages, static_cast<__nv_bfloat16*>(out), q_heads, kv_heads, head_dim, page_size,
-        window, scale, value_head, err);
+        window, scale, value_head, shape, err);
   } else {
     return b200_fail("paged_attention_plain: unknown dtype %d", dtype);
   }

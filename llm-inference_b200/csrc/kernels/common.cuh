@@ -208,6 +208,22 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return total;
 }
 
+// What an attention kernel does to a score beyond the scale: a soft cap, a learned bias by the key's distance and a
+// restriction to the query's own chunk of positions. All zero / null: nothing.
+struct ScoreShape {
+  float softcap;      // > 0: s <- softcap * tanh(s / softcap)
+  const float* bias;  // [q_heads][bias_reach + 1] by distance min(pos - key, bias_reach), added after the cap; null: none
+  int bias_reach;
+  int chunk;          // > 0: a query at `pos` sees keys from floor(pos / chunk) * chunk on only
+};
+
+// `s` is the scaled score, `bias_row` the query head's row of the bias table (or null), `distance` = pos - key >= 0.
+__device__ __forceinline__ float shaped_score(float s, const ScoreShape& shape, const float* bias_row, int distance) {
+  if (shape.softcap > 0.f) s = shape.softcap * tanhf(s / shape.softcap);
+  if (bias_row != nullptr) s += bias_row[min(distance, shape.bias_reach)];
+  return s;
+}
+
 // Offset (in elements) of row `row` of kv head `head` in page `page` of one layer's K or V
 // arena laid out [pages][kv_heads][page_size][head_dim].
 __device__ __forceinline__ int64_t kv_row_offset(int page, int head, int row, int kv_heads,

@@ -15,23 +15,26 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kMaxValuesPerThread = 8;  // rank <= 1024 in the plain kernel
 
-// The pair (u, v) of dims (2i, 2i + 1) at position p becomes (u cos a - v sin a, v cos a + u sin a),
-// a = p * inv_freq[i]; dims from `rot_dims` on pass unchanged.
-__device__ __forceinline__ void rotate_pair(float u, float v, int position, float inv_freq, float* ru, float* rv) {
+// The pair (u, v) of dims (2i, 2i + 1), or (i, i + rot_dims / 2) in the layout of halves, at position p becomes
+// (u cos a - v sin a, v cos a + u sin a), a = p * inv_freq[i], sine and cosine both times `magnitude`; dims from
+// `rot_dims` on pass unchanged.
+__device__ __forceinline__ void rotate_pair(float u, float v, int position, float inv_freq, float magnitude, float* ru, float* rv) {
   float s, c;
   sincosf(static_cast<float>(position) * inv_freq, &s, &c);
+  s *= magnitude;
+  c *= magnitude;
   *ru = u * c - v * s;
   *rv = v * c + u * s;
 }
 
-// One block per token. `proj` is the token's row of the fused input product:
-// [q: heads x (dim | rot_dim)] at q_offset, [latent (rank) | key part (rot_dim)] at kv_offset.
+// One block per token. The token's queries [heads x (dim | rot_dim)] start at q_offset of its row of `q_proj`, its
+// [latent (rank) | key part (rot_dim)] at kv_offset of its row of `proj` (the two may be one matrix).
 // Writes the normalised latent and the rotated key part to the token's cache row and the rotated
 // query parts to q_rot [tokens][heads][rot_dim].
 template <typename T>
-__global__ void latent_kv_write_kernel(const T* proj, int ld, int q_offset, int kv_offset, int heads, int dim, int rot_dim,
-                                       int rank, const float* __restrict__ norm_weight, float eps,
-                                       const float* __restrict__ inv_freq, int rot_dims, const int* positions,
+__global__ void latent_kv_write_kernel(const T* q_proj, int q_ld, const T* proj, int ld, int q_offset, int kv_offset, int heads, int dim,
+                                       int rot_dim, int rank, const float* __restrict__ norm_weight, float eps,
+                                       const float* __restrict__ inv_freq, int rot_dims, int halves, float magnitude, const int* positions,
                                        const int* token_seq, const int* block_table, int max_pages, int num_pages,
                                        T* arena, int page_size, int writes, T* q_rot, int* err) {
   __shared__ float scratch[32];
@@ -40,17 +43,19 @@ __global__ void latent_kv_write_kernel(const T* proj, int ld, int q_offset, int 
   const int t = blockIdx.x, tid = threadIdx.x;
   const int pos = positions[t];
   const T* row = proj + static_cast<int64_t>(t) * ld;
+  const T* q_row = q_proj + static_cast<int64_t>(t) * q_ld;
   const int half = rot_dims / 2;
   // queries: rotate each head's last rot_dim dims
   for (int idx = tid; idx < heads * (rot_dim - half); idx += blockDim.x) {
     const int h = idx / (rot_dim - half), i = idx % (rot_dim - half);
-    const T* src = row + q_offset + h * (dim + rot_dim) + dim;
+    const T* src = q_row + q_offset + h * (dim + rot_dim) + dim;
     T* dst = q_rot + (static_cast<int64_t>(t) * heads + h) * rot_dim;
     if (i < half) {
+      const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
       float u, v;
-      rotate_pair(to_f32<T>(src[2 * i]), to_f32<T>(src[2 * i + 1]), pos, inv_freq[i], &u, &v);
-      dst[2 * i] = from_f32<T>(u);
-      dst[2 * i + 1] = from_f32<T>(v);
+      rotate_pair(to_f32<T>(src[a]), to_f32<T>(src[b]), pos, inv_freq[i], magnitude, &u, &v);
+      dst[a] = from_f32<T>(u);
+      dst[b] = from_f32<T>(v);
     } else {
       dst[rot_dims + i - half] = src[rot_dims + i - half];
     }
@@ -74,10 +79,11 @@ __global__ void latent_kv_write_kernel(const T* proj, int ld, int q_offset, int 
   for (int i = tid; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(kv[i]) * inv * norm_weight[i]);
   for (int i = tid; i < rot_dim - half; i += blockDim.x) {
     if (i < half) {
+      const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
       float u, v;
-      rotate_pair(to_f32<T>(kv[rank + 2 * i]), to_f32<T>(kv[rank + 2 * i + 1]), pos, inv_freq[i], &u, &v);
-      dst[rank + 2 * i] = from_f32<T>(u);
-      dst[rank + 2 * i + 1] = from_f32<T>(v);
+      rotate_pair(to_f32<T>(kv[rank + a]), to_f32<T>(kv[rank + b]), pos, inv_freq[i], magnitude, &u, &v);
+      dst[rank + a] = from_f32<T>(u);
+      dst[rank + b] = from_f32<T>(v);
     } else {
       dst[rank + rot_dims + i - half] = kv[rank + rot_dims + i - half];
     }
@@ -175,9 +181,9 @@ latent_attention_plain_kernel(const T* q_lat, int64_t q_lat_token, int64_t q_lat
 
 }  // namespace
 
-B200_API int b200_latent_kv_write(const void* proj, int ld, int q_offset, int kv_offset, int tokens, int heads, int dim,
-                                  int rot_dim, int rank, const float* norm_weight, float eps, const float* inv_freq,
-                                  int rot_dims, const int* positions, const int* token_seq, const int* block_table,
+B200_API int b200_latent_kv_write(const void* q_proj, int q_ld, const void* proj, int ld, int q_offset, int kv_offset, int tokens, int heads,
+                                  int dim, int rot_dim, int rank, const float* norm_weight, float eps, const float* inv_freq,
+                                  int rot_dims, int halves, float magnitude, const int* positions, const int* token_seq, const int* block_table,
                                   int max_pages, int num_pages, void* arena, int page_size, int writes, void* q_rot,
                                   int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
@@ -187,14 +193,15 @@ B200_API int b200_latent_kv_write(const void* proj, int ld, int q_offset, int kv
   B200_REQUIRE(page_size > 0 && max_pages > 0, "latent_kv_write: bad geometry");
   const int threads = rank >= 512 ? 256 : 128;
   if (dtype == DTYPE_F32) {
-    launch_kernel(latent_kv_write_kernel<float>, dim3(tokens), dim3(threads), 0, stream, static_cast<const float*>(proj), ld,
-                  q_offset, kv_offset, heads, dim, rot_dim, rank, norm_weight, eps, inv_freq, rot_dims, positions, token_seq,
+    launch_kernel(latent_kv_write_kernel<float>, dim3(tokens), dim3(threads), 0, stream, static_cast<const float*>(q_proj), q_ld,
+                  static_cast<const float*>(proj), ld, q_offset, kv_offset, heads, dim, rot_dim, rank, norm_weight, eps, inv_freq, rot_dims,
+                  halves, magnitude, positions, token_seq,
                   block_table, max_pages, num_pages, static_cast<float*>(arena), page_size, writes, static_cast<float*>(q_rot),
                   err);
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(latent_kv_write_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
-                  static_cast<const __nv_bfloat16*>(proj), ld, q_offset, kv_offset, heads, dim, rot_dim, rank, norm_weight, eps,
-                  inv_freq, rot_dims, positions, token_seq, block_table, max_pages, num_pages,
+                  static_cast<const __nv_bfloat16*>(q_proj), q_ld, static_cast<const __nv_bfloat16*>(proj), ld, q_offset, kv_offset, heads,
+                  dim, rot_dim, rank, norm_weight, eps, inv_freq, rot_dims, halves, magnitude, positions, token_seq, block_table, max_pages, num_pages,
                   static_cast<__nv_bfloat16*>(arena), page_size, writes, static_cast<__nv_bfloat16*>(q_rot), err);
   } else {
     return b200_fail("latent_kv_write: unknown dtype %d", dtype);

@@ -5,10 +5,12 @@
 // Router (one warp per token, all 32-bit): s = sigmoid(z); the experts form `groups` equal groups of
 // neighbours, a group scores the sum of its two largest s, only experts of the `keep` best groups can
 // be chosen; the `top` largest s among them are chosen (ties: the lower index), and their weights are
-// s / (sum of the chosen s + 1e-20) * scale.
+// s / (sum of the chosen s + 1e-20) * scale. A second kind of router (`softmax_chosen`) scores an expert by its logit
+// itself, z plus a learned bias per expert, chooses the `top` largest and weighs them by the softmax over the chosen
+// logits only, times scale. A bias may be given to either kind.
 //
 // Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g sigmoid(1.702 g) (u + 1),
-// output W_down y.
+// output W_down y. A limit of zero means the unclamped form y = silu(W_gate h) * (W_up h).
 //
 // Grouping: every (token, choice) pair is a slot. `moe_sort` (one block) counts the slots of each
 // expert, gives each expert a run of whole tiles of `tile_rows` sorted places (kTileM, or four times
@@ -29,6 +31,7 @@ constexpr int kGemmThreads = 256;  // 8 row groups of 4 rows x 32 columns
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
 __device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+  if (limit <= 0.f) return g * sigmoid_f(g) * u;  // no clamps: silu(g) * u
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * sigmoid_f(1.702f * g) * (u + 1.f);
@@ -49,8 +52,8 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
 
 // z [tokens][experts] -> ids [tokens][top], weights [tokens][top]. Shared memory per warp:
 // experts scores + groups group scores.
-__global__ void moe_route_kernel(const float* z, int tokens, int experts, int groups, int keep, int top, float scale, int* ids,
-                                 float* weights) {
+__global__ void moe_route_kernel(const float* z, const float* __restrict__ bias, int softmax_chosen, int tokens, int experts, int groups,
+                                 int keep, int top, float scale, int* ids, float* weights) {
   extern __shared__ float route_smem[];
   wait_for_predecessor();
   let_successor_start();
@@ -60,7 +63,10 @@ __global__ void moe_route_kernel(const float* z, int tokens, int experts, int gr
   float* s = route_smem + warp * (experts + groups);
   float* gs = s + experts;
   const int size = experts / groups;
-  for (int e = lane; e < experts; e += 32) s[e] = sigmoid_f(z[static_cast<int64_t>(t) * experts + e]);
+  for (int e = lane; e < experts; e += 32) {
+    const float logit = z[static_cast<int64_t>(t) * experts + e] + (bias ? bias[e] : 0.f);
+    s[e] = softmax_chosen ? logit : sigmoid_f(logit);
+  }
   __syncwarp();
   for (int g = lane; g < groups; g += 32) {
     float first = -INFINITY, second = -INFINITY;
@@ -108,6 +114,27 @@ __global__ void moe_route_kernel(const float* z, int tokens, int experts, int gr
     }
     if (lane == 0) s[at] = -INFINITY;
     __syncwarp();
+  }
+  if (softmax_chosen) {
+    // The first choice is the largest logit. exp(logit - largest) over the chosen, then their share of the sum.
+    const float largest = __shfl_sync(0xffffffffu, mine, 0);
+    float e_mine = lane < top ? expf(mine - largest) : 0.f;
+    float total = warp_sum(e_mine);
+    if (lane == 0)
+      for (int j = 32; j < top; ++j) {
+        const float e = expf(weights[static_cast<int64_t>(t) * top + j] - largest);
+        weights[static_cast<int64_t>(t) * top + j] = e;
+        total += e;
+      }
+    total = __shfl_sync(0xffffffffu, total, 0);
+    const float share = scale / total;
+    if (lane < top) {
+      ids[static_cast<int64_t>(t) * top + lane] = mine_id;
+      weights[static_cast<int64_t>(t) * top + lane] = e_mine * share;
+    }
+    if (lane == 0)
+      for (int j = 32; j < top; ++j) weights[static_cast<int64_t>(t) * top + j] *= share;
+    return;
   }
   const float factor = scale / (sum + 1e-20f);
   if (lane < top) {
@@ -501,8 +528,8 @@ __global__ void clamped_glu_wide_kernel(const __nv_bfloat16* gate_up, int64_t ro
 
 B200_API int b200_moe_tile_rows() { return kTileM; }
 
-B200_API int b200_moe_route(const float* z, int tokens, int experts, int groups, int keep, int top, float scale, int* ids, float* weights,
-                            cudaStream_t stream) {
+B200_API int b200_moe_route(const float* z, const float* bias, int softmax_chosen, int tokens, int experts, int groups, int keep, int top,
+                            float scale, int* ids, float* weights, cudaStream_t stream) {
   if (tokens == 0) return 0;
   B200_REQUIRE(tokens > 0 && experts > 0 && groups > 0 && experts % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
                    top <= keep * (experts / groups),
@@ -510,8 +537,8 @@ B200_API int b200_moe_route(const float* z, int tokens, int experts, int groups,
   const int warps = 4;
   const size_t smem = sizeof(float) * warps * (experts + groups);
   B200_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts do not fit shared memory", experts);
-  launch_kernel(moe_route_kernel, dim3((tokens + warps - 1) / warps), dim3(32 * warps), smem, stream, z, tokens, experts, groups, keep,
-                top, scale, ids, weights);
+  launch_kernel(moe_route_kernel, dim3((tokens + warps - 1) / warps), dim3(32 * warps), smem, stream, z, bias, softmax_chosen, tokens, experts,
+                groups, keep, top, scale, ids, weights);
   return b200_check_launch("moe_route");
 }
 
@@ -540,7 +567,7 @@ B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* plac
                               int max_tiles, int tile_rows, int top, int width, int ff, float limit, void* act, int dtype, int use_mma,
                               cudaStream_t stream) {
   if (max_tiles == 0) return 0;
-  B200_REQUIRE(max_tiles > 0 && top > 0 && width > 0 && ff > 0 && limit > 0.f, "moe_gate_up: bad sizes");
+  B200_REQUIRE(max_tiles > 0 && top > 0 && width > 0 && ff > 0 && limit >= 0.f, "moe_gate_up: bad sizes");
   const bool mma = dtype == DTYPE_BF16 && use_mma && b200_moe_mma_supported(width, ff) && aligned16(h) && aligned16(weight) && aligned16(act);
   B200_REQUIRE(tile_rows == kTileM || (mma && tile_rows == kTileM * kWideTiles), "moe_gate_up: tiles of %d rows are not taken here", tile_rows);
   const dim3 grid(max_tiles, (ff + kTileN - 1) / kTileN);
@@ -615,7 +642,7 @@ B200_API int b200_moe_combine(const float* expert_out, const float* weights, con
 
 B200_API int b200_clamped_glu(const void* gate_up, int rows, int ff, float limit, void* out, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  B200_REQUIRE(rows > 0 && ff > 0 && limit > 0.f, "clamped_glu: bad sizes");
+  B200_REQUIRE(rows > 0 && ff > 0 && limit >= 0.f, "clamped_glu: bad sizes");
   const int threads = 256;
   const int64_t total = static_cast<int64_t>(rows) * ff;
   const int64_t want = (total + threads - 1) / threads;

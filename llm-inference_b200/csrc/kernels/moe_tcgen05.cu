@@ -101,6 +101,7 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
 }
 
 __device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+  if (limit <= 0.f) return g * (1.f / (1.f + expf(-g))) * u;  // a limit of zero: the unclamped form silu(g) * u
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
@@ -344,7 +345,7 @@ B200_API int b200_moe_product_tcgen05(const void* weight, const void* x, const i
   if (max_tiles == 0) return 0;
   B200_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && experts > 0 && rows_per_expert > 0 && n_total > 0 && K > 0 && K % 8 == 0 && (mats == 1 || mats == 2),
                "moe_product_tcgen05: bad sizes");
-  B200_REQUIRE(mats == 1 || (second_offset > 0 && second_offset + n_total <= rows_per_expert && limit > 0.f), "moe_product_tcgen05: bad second matrix");
+  B200_REQUIRE(mats == 1 || (second_offset > 0 && second_offset + n_total <= rows_per_expert && limit >= 0.f), "moe_product_tcgen05: bad second matrix");
   B200_REQUIRE(reinterpret_cast<uintptr_t>(weight) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0, "moe_product_tcgen05: operands must be 16-byte aligned");
   // Two stages: 96 KB (gate and up) or 64 KB (down) a block, so that two or three blocks share an SM and one's epilogue runs
   // beside the others' products. Measured on a B200 (2,048 tokens, width 3,584, 32 experts, 4 a token): 630 us for both

@@ -55,9 +55,10 @@ _SIGNATURES: dict[str, list] = {
     "b200_paged_attention_plain": [c_void_p] * 6
     + [c_int, c_int, c_void_p]
     + [c_int] * 6
-    + [c_float, c_int, c_int, c_void_p, c_void_p],
+    + [c_float, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
-    "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
+                                   c_void_p, c_void_p, c_void_p],
     "b200_paged_decode_attention_tma": [c_void_p] * 8 + [c_int] * 8 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "b200_flash_prefill_tcgen05": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_void_p, c_void_p],
     "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p],
@@ -74,8 +75,8 @@ _SIGNATURES: dict[str, list] = {
     "b200_grouped_rmsnorm": [c_void_p] * 3 + [c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "b200_embedding_scaled": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200_poly_norm": [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
-    "b200_latent_kv_write": [c_void_p] + [c_int] * 8 + [c_void_p, c_float, c_void_p, c_int] + [c_void_p] * 3 + [c_int, c_int,
-                             c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    "b200_latent_kv_write": [c_void_p, c_int, c_void_p] + [c_int] * 8 + [c_void_p, c_float, c_void_p, c_int, c_int, c_float] + [c_void_p] * 3
+                            + [c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
     "b200_latent_attention_plain": [c_void_p, c_int64, c_int64] + [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_int64, c_int64] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p],
     "b200_latent_attention_mma": [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 3
@@ -96,7 +97,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_norm_kv_write": [c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_int] + [c_void_p] * 5 + [c_int] * 9 + [c_float, c_int, c_int,
                            c_void_p, c_void_p],
     "b200_head_gate": [c_void_p, c_void_p] + [c_int] * 6 + [c_void_p, c_int, c_void_p],
-    "b200_moe_route": [c_void_p] + [c_int] * 5 + [c_float, c_void_p, c_void_p, c_void_p],
+    "b200_moe_route": [c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_void_p, c_void_p, c_void_p],
     "b200_moe_sort": [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4,
     "b200_moe_gate_up": [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p, c_int, c_int, c_void_p],
     "b200_moe_down": [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_int, c_int, c_void_p],
@@ -111,6 +112,13 @@ _SIGNATURES: dict[str, list] = {
                                  + [c_void_p] * 7 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 10 + [c_void_p, c_void_p],
     "b200_mix_heads_gate": [c_void_p] * 3 + [c_int] * 6 + [c_void_p, c_int, c_void_p],
     "b200_pair_norm_add": [c_void_p] * 6 + [c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_layernorm": [c_void_p] * 5 + [c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_embedding_layernorm": [c_void_p] * 3 + [c_float, c_void_p] + [c_int] * 4 + [c_void_p, c_void_p],
+    "b200_rms_rows": [c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_void_p, c_int64, c_int, c_void_p],
+    "b200_sigmoid_mul": [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_scale_values": [c_void_p, c_int64, c_float, c_void_p],
+    "b200_qk_norm_rope_write": [c_void_p, c_int] + [c_void_p] * 3 + [c_float, c_void_p, c_int, c_float, c_int] + [c_void_p] * 4
+                               + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 9 + [c_void_p, c_void_p],
     "b200_embedding_bigram": [c_void_p] * 9 + [c_int, c_int64, c_int64, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_void_p],
 }
 

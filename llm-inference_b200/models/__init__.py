@@ -1,3 +1,3 @@
 """Architectures this engine knows; importing the package registers them."""
 
-from . import gunedra, lerorax, qwen2, tunadra  # noqa: F401
+from . import gunedra, lerorax, qwen2, tunadra, zetizen  # noqa: F401

@@ -1,4 +1,4 @@
-from . import attention, block, delta_rule, embedding, feed_forward, gated_attention, hyper, latent_attention, mingru, mixed_attention, norms, parallel, positions, wkv  # noqa: F401  (register parts)
+from . import attention, block, delta_rule, embedding, feed_forward, gated_attention, hyper, latent_attention, mingru, mixed_attention, norms, parallel, positions, shaped_attention, wkv  # noqa: F401  (register parts)
 from .base import (
     CacheSpecs,
     KVCacheSpec,

@@ -28,8 +28,13 @@ def attend(
     head_dim: int,
     scale: float,
     value_head: int = -1,
+    shape: ops.ScoreShape = ops.NO_SHAPE,
 ) -> None:
-    """``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
+    """``shape``: a soft cap, a bias by distance and a chunk of visible keys (``ops.ScoreShape``); the plain kernel and the
+    mma.sync kernels take it, so shaped attention of prompt portions runs the mma.sync prefill form and decoded tokens the
+    cp.async split-key kernel, whatever the head size.
+
+    ``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
     instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head); the
     mma.sync kernels take it (values by cp.async from the other head's rows of the same page) and so does the
     tcgen05 prefill kernel (the value boxes' row coordinate names the other head); the TMA decode kernel does not."""
@@ -42,20 +47,22 @@ def attend(
     if not tuned:
         if choice in ("flash", "tcgen05"):
             raise ops.KernelError("the tensor-core attention kernels do not take this shape or dtype")
-        ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale, value_head=value_head)
+        ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale, value_head=value_head, shape=shape)
         return
     decode_seqs = ctx.num_decode_seqs
     if decode_seqs and not ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=True):
         decode_seqs = 0  # more than 16 query heads per kv head: the prefill form handles one-token runs too
     if decode_seqs:
         reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
-        tma = value_head < 0 and ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+        if shape.chunk:
+            reach = min(reach, shape.chunk)  # a decoded token sees its own chunk at most
+        tma = value_head < 0 and not shape and ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
         splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(decode_seqs, kv_heads, reach, tma, ops.sm_count(ctx))
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
-            first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head,
+            first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head, shape=shape,
         )
-    if ctx.num_seqs > decode_seqs and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+    if ctx.num_seqs > decode_seqs and not shape and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
         ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
     ):
         ops.paged_prefill_attention_tcgen05(
@@ -68,6 +75,7 @@ def attend(
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len, value_head=value_head,
+            shape=shape,
         )
 
 

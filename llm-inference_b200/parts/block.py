@@ -152,5 +152,43 @@ class PostNormResidualBlock(Part):
         return None
 
 
+class ParallelResidualBlock(Part):
+    """``h = norm(x); x += mixer(h) + feed_forward(h)``: one norm, and both sublayers read its output
+    (``feed_forward`` may be None). The two outputs travel on together as :class:`ops.BranchSum` and the norm kernel
+    that runs next (the following layer's, or the model's last) adds them into the stream in 32-bit, as the pre-norm
+    block passes its pending branch output on. The feed-forward is built to write another buffer than the mixer."""
+
+    def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec | None, norm: PartSpec) -> None:
+        self.mixer_norm = build_part("norm", norm)
+        self.mixer = build_part("mixer", mixer)
+        self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward) if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self.parts)
+
+    def tensor_specs(self):
+        return [spec for part in self.parts for spec in part.tensor_specs()]
+
+    def load(self, tensors, dtype, device) -> None:
+        for part in self.parts:
+            part.load(tensors, dtype, device)
+
+    def weight_bytes(self) -> int:
+        return sum(part.weight_bytes() for part in self.parts)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx: StepContext, cache: CacheView | None, x: torch.Tensor, delta):
+        h = self.mixer_norm.forward(ctx, x, delta)
+        a = self.mixer.forward(ctx, cache, h)
+        if self.feed_forward is None:
+            return a
+        b = self.feed_forward.forward(ctx, h)
+        if a.data_ptr() == b.data_ptr():
+            raise ValueError("the mixer and the feed-forward of a parallel block must write different buffers")
+        return ops.BranchSum(a, b)
+
+
+register_part("block", "parallel_residual", ParallelResidualBlock)
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
 register_part("block", "post_norm_residual", PostNormResidualBlock)

@@ -41,6 +41,30 @@ class TokenEmbedding(Part):
         return ops.embedding_scaled(ctx, self.table, self.scale, x, cast)
 
 
+class NormedEmbedding(Part):
+    """``x[t] = layer norm of table[token[t]]`` (mean taken off, a weight ``norm_name`` and no bias), in 32-bit, as the
+    residual stream of the new tokens: gather and norm are one kernel."""
+
+    def __init__(self, *, name: str, norm_name: str, vocab_size: int, hidden_size: int, eps: float) -> None:
+        self.name, self.norm_name, self.vocab_size, self.hidden_size, self.eps = name, norm_name, vocab_size, hidden_size, float(eps)
+        self.table: torch.Tensor | None = None
+        self.norm_weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size)), TensorSpec(self.norm_name, (self.hidden_size,), init="one_plus_normal")]
+
+    def load(self, tensors, dtype, device) -> None:
+        self.table = tensors[self.name].to(device=device, dtype=dtype).contiguous()
+        self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return 0  # a step reads only its tokens' rows
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        x = ctx.buffer("residual", (ctx.num_tokens, self.hidden_size), torch.float32)
+        return ops.embedding_layernorm(ctx, self.table, self.norm_weight, self.eps, x)
+
+
 class SinusoidEmbedding(Part):
     """``x[t] = table[token[t]] * scale + e(p)`` with ``e(p)[2i] = sin(p f_i)``, ``e(p)[2i + 1] = cos(p f_i)``,
     ``f_i = base^(-2i / hidden)`` and ``p`` the token's position in its request; the sum is 32-bit and fills
@@ -113,9 +137,10 @@ class OutputHead(Part):
     the checkpoint need not hold a tensor of its own (python/instinct/export.py:38-41)."""
 
     def __init__(self, *, name: str, vocab_size: int, hidden_size: int, tied_to: str | None = None, suffix: str = ".weight",
-                 softcap: float | None = None) -> None:
+                 softcap: float | None = None, scale: float | None = None) -> None:
         self.name, self.vocab_size, self.hidden_size, self.tied_to = name, vocab_size, hidden_size, tied_to
         self.suffix = suffix
+        self.scale = float(scale) if scale is not None and float(scale) != 1.0 else None  # logits <- logits * scale (before any cap)
         self.softcap = float(softcap) if softcap else None  # logits <- softcap * tanh(logits / softcap)
         self.weight: torch.Tensor | None = None
 
@@ -139,10 +164,13 @@ class OutputHead(Part):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         logits = ops.linear(ctx, h, self.weight, ctx.buffer("logits", (h.shape[0], self.vocab_size), torch.float32, per_token=False))
+        if self.scale is not None:
+            ops.scale_values(ctx, logits, self.scale)
         return ops.softcap(ctx, logits, self.softcap) if self.softcap else logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "normed_embedding", NormedEmbedding)
 register_part("embedding", "sinusoid_embedding", SinusoidEmbedding)
 register_part("embedding", "bigram_embedding", BigramEmbedding)
 register_part("head", "linear_head", OutputHead)

@@ -121,15 +121,27 @@ class RoutedExperts(Part):
     ``s`` among them are chosen and weighted ``s / (sum of the chosen s + 1e-20) * route_scale``. The output
     is the weighted sum of the chosen experts' outputs plus the shared expert's.
 
+    ``router="softmax_chosen"`` is another router: the ``top`` largest logits ``W_router h`` (+ ``router.b`` with
+    ``router_bias``) are chosen and weighted by the softmax over the chosen logits alone (times ``route_scale``); it has no
+    groups. A ``limit`` of zero makes an expert ``W_down (silu(W_gate h) * (W_up h))``, without clamps. ``out_name`` is the
+    buffer the result goes to (a layer that runs its feed-forward beside its mixer gives it one of its own).
+
     The experts' matrices are stacked (``[experts, 2 ff, hidden]`` with the gate rows first, and
     ``[experts, hidden, ff]``); a step sorts its (token, choice) pairs by expert and the two products
     walk the sorted runs, so only chosen experts' weights are read. Tensor names: ``prefix + router |
     e<j>.{gate,up,down} | shared.{gate,up,down}``."""
 
     def __init__(self, *, prefix: str, hidden_size: int, experts: int, top: int, intermediate_size: int, limit: float,
-                 route_scale: float, group_count: int = 1, group_keep: int = 1, shared_size: int | None = None,
-                 shared_limit: float | None = None) -> None:
+                 route_scale: float = 1.0, group_count: int = 1, group_keep: int = 1, shared_size: int | None = None,
+                 shared_limit: float | None = None, router: str = "sigmoid_groups", router_bias: bool = False,
+                 out_name: str = "branch") -> None:
+        if router not in ("sigmoid_groups", "softmax_chosen"):
+            raise ValueError(f"router={router!r} must be 'sigmoid_groups' or 'softmax_chosen'")
+        if router == "softmax_chosen" and (group_count != 1 or group_keep != 1):
+            raise ValueError("the router that weighs by a softmax over the chosen logits has no groups")
         self.prefix, self.hidden_size = prefix, hidden_size
+        self.router, self.router_bias, self.out_name = router, bool(router_bias), out_name
+        self.b_router = None
         self.experts, self.top, self.intermediate_size, self.limit = int(experts), int(top), int(intermediate_size), float(limit)
         self.route_scale, self.group_count, self.group_keep = float(route_scale), int(group_count), int(group_keep)
         self.shared_size = int(shared_size) if shared_size else 0
@@ -139,6 +151,8 @@ class RoutedExperts(Part):
     def tensor_specs(self) -> list[TensorSpec]:
         p, h, i = self.prefix, self.hidden_size, self.intermediate_size
         specs = [TensorSpec(p + "router", (self.experts, h))]
+        if self.router_bias:
+            specs.append(TensorSpec(p + "router.b", (self.experts,)))
         for e in range(self.experts):
             specs += [TensorSpec(f"{p}e{e}.gate", (i, h)), TensorSpec(f"{p}e{e}.up", (i, h)), TensorSpec(f"{p}e{e}.down", (h, i))]
         if self.shared_size:
@@ -153,6 +167,8 @@ class RoutedExperts(Part):
             return tensors[p + name].to(device=device, dtype=dtype)
 
         self.w_router = get("router").contiguous()
+        if self.router_bias:
+            self.b_router = tensors[p + "router.b"].to(device=device, dtype=torch.float32).contiguous()
         self.w_gate_up = torch.stack([torch.cat([get(f"e{e}.gate"), get(f"e{e}.up")]) for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([get(f"e{e}.down") for e in range(self.experts)]).contiguous()
         if self.shared_size:
@@ -172,7 +188,8 @@ class RoutedExperts(Part):
         # the step (expert load statistics, tests), also when the step was replayed from a captured graph.
         ids = ctx.buffer("moe_ids:" + self.prefix, (t, self.top), torch.int32)
         weights = ctx.buffer("moe_weights", (t, self.top), torch.float32)
-        ops.moe_route(ctx, logits, self.group_count, self.group_keep, self.top, self.route_scale, ids, weights)
+        ops.moe_route(ctx, logits, self.group_count, self.group_keep, self.top, self.route_scale, ids, weights, bias=self.b_router,
+                      softmax_chosen=self.router == "softmax_chosen")
         expert_out = ops.moe_experts(
             ctx, h, ids, self.w_gate_up, self.w_down, self.limit, ctx.buffer("moe_expert_out", (t * self.top, width), torch.float32, per_token=False)
         )
@@ -181,7 +198,7 @@ class RoutedExperts(Part):
             gate_up = ops.linear(ctx, h, self.w_shared_gate_up, ctx.buffer("gate_up", (t, 2 * self.shared_size)))
             act = ops.clamped_glu(ctx, gate_up, self.shared_limit, ctx.buffer("act", (t, self.shared_size)))
             shared = ops.linear(ctx, act, self.w_shared_down, ctx.buffer("moe_shared", (t, width)))
-        return ops.moe_combine(ctx, expert_out, weights, shared, ctx.buffer("branch", (t, width)))
+        return ops.moe_combine(ctx, expert_out, weights, shared, ctx.buffer(self.out_name, (t, width)))
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -24,12 +24,23 @@ class LatentAttention(Part):
     denominator also holds ``exp(sink[n])`` (no key, no value, not scaled); with ``gate`` a head's
     output is multiplied by ``sigmoid(W_g h)[n]``. Then ``W_o`` on the concatenated heads.
 
-    The query, latent and gate projections are one matrix product. Tensor names are
-    ``prefix + q | dkv | dkv.norm | uk | uv | sink | g | o``."""
+    With ``q_rank`` the queries come out of a latent of their own: ``q = W_uq rmsnorm(W_dq h)`` (weight ``dq.norm``)
+    instead of ``W_q h``. With ``gate_per="element"`` the gate is one number per output number: the concatenated heads are
+    multiplied element by element by ``sigmoid(W_g h)`` (``W_g`` is ``[heads * vdim, hidden]``) after the expansion by
+    ``W_uv``. The position part may pair neighbours or halves of the rotated part.
+
+    The query (or its latent), latent and gate projections are one matrix product. Tensor names are
+    ``prefix + q | dq | dq.norm | uq | dkv | dkv.norm | uk | uv | sink | g | o``."""
 
     def __init__(self, *, prefix: str, hidden_size: int, heads: int, dim: int, rot_dim: int, vdim: int, rank: int,
-                 scale: float, eps: float, position: PartSpec, sink: bool = True, gate: bool = True, window: int = 0) -> None:
-        self.prefix, self.hidden_size = prefix, hidden_size
+                 scale: float, eps: float, position: PartSpec, sink: bool = True, gate: bool = True, window: int = 0,
+                 q_rank: int | None = None, gate_per: str = "head", out_name: str = "branch") -> None:
+        if gate_per not in ("head", "element"):
+            raise ValueError(f"gate_per={gate_per!r} must be 'head' or 'element'")
+        self.prefix, self.hidden_size, self.out_name = prefix, hidden_size, out_name
+        self.q_rank = int(q_rank) if q_rank else 0
+        self.gate_per_element = bool(gate) and gate_per == "element"
+        self.w_uq = self.q_norm_weight = None
         self.heads, self.dim, self.rot_dim, self.vdim, self.rank = heads, dim, rot_dim, vdim, rank
         self.scale, self.eps, self.window = float(scale), float(eps), int(window)
         self.has_sink, self.has_gate = bool(sink), bool(gate)
@@ -42,8 +53,13 @@ class LatentAttention(Part):
 
     def tensor_specs(self) -> list[TensorSpec]:
         p, d = self.prefix, self.hidden_size
-        specs = [
-            TensorSpec(p + "q", (self.heads * (self.dim + self.rot_dim), d)),
+        q_width = self.heads * (self.dim + self.rot_dim)
+        if self.q_rank:
+            specs = [TensorSpec(p + "dq", (self.q_rank, d)), TensorSpec(p + "dq.norm", (self.q_rank,), init="one_plus_normal"),
+                     TensorSpec(p + "uq", (q_width, self.q_rank))]
+        else:
+            specs = [TensorSpec(p + "q", (q_width, d))]
+        specs += [
             TensorSpec(p + "dkv", (self.rank + self.rot_dim, d)),
             TensorSpec(p + "dkv.norm", (self.rank,), init="one_plus_normal"),
             TensorSpec(p + "uk", (self.heads * self.dim, self.rank)),
@@ -53,12 +69,15 @@ class LatentAttention(Part):
         if self.has_sink:
             specs.append(TensorSpec(p + "sink", (self.heads,)))
         if self.has_gate:
-            specs.append(TensorSpec(p + "g", (self.heads, d)))
+            specs.append(TensorSpec(p + "g", (self.heads * self.vdim if self.gate_per_element else self.heads, d)))
         return specs + self.position.tensor_specs()
 
     def load(self, tensors, dtype, device) -> None:
         p = self.prefix
-        names = ["q", "dkv"] + (["g"] if self.has_gate else [])
+        names = ["dq" if self.q_rank else "q", "dkv"] + (["g"] if self.has_gate else [])
+        if self.q_rank:
+            self.w_uq = tensors[p + "uq"].to(device=device, dtype=dtype).contiguous()
+            self.q_norm_weight = tensors[p + "dq.norm"].to(device=device, dtype=torch.float32).contiguous()
         self.w_in = torch.cat([tensors[p + n].to(device=device, dtype=dtype) for n in names]).contiguous()
         # [heads, rank, dim]: the product that carries a query into the latent space reads W_uk[n]^T.
         self.w_uk_t = tensors[p + "uk"].to(device=device, dtype=dtype).view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
@@ -69,7 +88,7 @@ class LatentAttention(Part):
         self.position.load(tensors, dtype, device)
 
     def weight_bytes(self) -> int:
-        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_uk_t, self.w_uv, self.w_o))
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.w_uq) if w is not None)
 
     def forward(self, ctx: StepContext, cache: CacheView, h: torch.Tensor) -> torch.Tensor:
         t, heads, rank, rot = ctx.num_tokens, self.heads, self.rank, self.rot_dim
@@ -77,15 +96,25 @@ class LatentAttention(Part):
         width = self.w_in.shape[0]
         proj = ops.linear(ctx, h, self.w_in, ctx.buffer("latent_in", (t, width)))
         q_rot = ctx.buffer("latent_q_rot", (t, heads * rot))
-        self.position.apply_latent(ctx, cache, proj, 0, q_width, heads, self.dim, rank, self.norm_weight, self.eps, q_rot)
-        q_plain = proj[:, :q_width].view(t, heads, self.dim + rot)[:, :, : self.dim].transpose(0, 1)
+        if self.q_rank:
+            # queries through their own latent: norm of the first q_rank columns, then one more product
+            latent_q = ops.rms_rows(ctx, proj[:, : self.q_rank], self.q_norm_weight, self.eps, ctx.buffer("latent_cq", (t, self.q_rank)))
+            queries = ops.linear(ctx, latent_q, self.w_uq, ctx.buffer("latent_queries", (t, q_width)))
+            kv_offset = self.q_rank
+            self.position.apply_latent(ctx, cache, proj, 0, kv_offset, heads, self.dim, rank, self.norm_weight, self.eps, q_rot, q_proj=queries)
+        else:
+            queries, kv_offset = proj[:, :q_width], q_width
+            self.position.apply_latent(ctx, cache, proj, 0, kv_offset, heads, self.dim, rank, self.norm_weight, self.eps, q_rot)
+        q_plain = queries.view(t, heads, self.dim + rot)[:, :, : self.dim].transpose(0, 1)
         q_lat = ops.linear_per_head(ctx, q_plain, self.w_uk_t, ctx.buffer("latent_q", (heads, t, rank)))
-        gate = proj[:, q_width + rank + rot :] if self.has_gate else None
+        gate = proj[:, kv_offset + rank + rot :] if self.has_gate else None
         mixed = ctx.buffer("latent_out", (heads, t, rank))
-        self.attend(ctx, cache, q_lat, q_rot, gate, mixed)
+        self.attend(ctx, cache, q_lat, q_rot, None if self.gate_per_element else gate, mixed)
         attn = ctx.buffer("attn", (t, heads * self.vdim))
         ops.linear_per_head(ctx, mixed, self.w_uv, attn.view(t, heads, self.vdim).transpose(0, 1))
-        return ops.linear(ctx, attn, self.w_o, ctx.buffer("branch", (t, self.hidden_size)))
+        if self.gate_per_element:
+            attn = ops.sigmoid_mul(ctx, attn, gate, ctx.buffer("attn_gated", (t, heads * self.vdim)))
+        return ops.linear(ctx, attn, self.w_o, ctx.buffer(self.out_name, (t, self.hidden_size)))
 
     def attend(self, ctx: StepContext, cache: CacheView, q_lat, q_rot, gate, out) -> None:
         from . import attention_dispatch

@@ -105,5 +105,35 @@ class GroupedRMSNorm(Part):
         ops.branch_norm_add(ctx, x_in, branch, self.weight, scale, mult, self.groups, self.eps, x_out, **more)
 
 
+class LayerNorm(Part):
+    """``y = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * weight`` with ``v = x + delta``, a weight and no bias,
+    all in 32-bit; the add into the residual stream is part of the same kernel. ``delta`` may be one branch output or
+    an :class:`ops.BranchSum` (two sublayers that read the same normed rows). The tensor is ``name`` itself."""
+
+    foldable = False
+
+    def __init__(self, *, name: str, hidden_size: int, eps: float) -> None:
+        self.name, self.hidden_size, self.eps = name, hidden_size, float(eps)
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.hidden_size,), init="one_plus_normal")]
+
+    def load(self, tensors, dtype, device) -> None:
+        self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * 4
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, rows: torch.Tensor | None = None, out_name: str = "normed",
+                folded_ok: bool = False) -> torch.Tensor:
+        if isinstance(delta, ops.FoldedRows):
+            delta = None  # the stream is already up to date
+        count = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (count, self.hidden_size), per_token=rows is None)
+        return ops.layernorm(ctx, x, delta, self.weight, self.eps, out, rows)
+
+
+register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

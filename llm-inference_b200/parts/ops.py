@@ -347,6 +347,31 @@ def rope_kv_write(
     return q_out
 
 
+@dataclass(frozen=True)
+class ScoreShape:
+    """What an attention kernel does to a scaled score before the softmax, beyond masking the future: ``softcap``
+    (``s <- softcap * tanh(s / softcap)``), ``bias`` (float32 ``[q_heads, reach + 1]`` on the device: the row of the
+    query head at ``min(position - key, reach)`` is added after the cap) and ``chunk`` (a query sees only keys from
+    ``floor(position / chunk) * chunk`` on). The plain kernel and the ``mma.sync`` kernels take it."""
+
+    softcap: float = 0.0
+    bias: torch.Tensor | None = None
+    chunk: int = 0
+
+    def __bool__(self) -> bool:
+        return bool(self.softcap > 0.0 or self.bias is not None or self.chunk > 0)
+
+    def arguments(self, q_heads: int) -> list:
+        if self.bias is not None:
+            _need(self.bias.dtype == torch.float32 and self.bias.dim() == 2 and self.bias.shape[0] == q_heads and self.bias.is_contiguous(),
+                  "attention: the bias by distance is float32 [q_heads, reach + 1]")
+        reach = self.bias.shape[1] - 1 if self.bias is not None else 0
+        return [c_float(self.softcap), ptr(self.bias), c_int(reach), c_int(self.chunk)]
+
+
+NO_SHAPE = ScoreShape()
+
+
 def paged_attention_plain(
     ctx: StepContext,
     cache: CacheView,
@@ -360,6 +385,7 @@ def paged_attention_plain(
     first_token: int = 0,
     num_tokens: int | None = None,
     value_head: int = -1,
+    shape: ScoreShape = NO_SHAPE,
 ) -> torch.Tensor:
     """Attention of rows ``first_token .. first_token + num_tokens`` of the step over the cache. With
     ``value_head`` >= 0 every query head's weights are applied to the values of that kv head."""
@@ -377,7 +403,8 @@ def paged_attention_plain(
         ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
         ptr(out) if first_token == 0 else _offset(out, first_token * row_bytes),
         c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size),
-        c_int(cache.window), c_float(scale), c_int(value_head), c_int(dtype_code(q.dtype)), ptr(ctx.err), ctx.stream,
+        c_int(cache.window), c_float(scale), c_int(value_head), *shape.arguments(q_heads), c_int(dtype_code(q.dtype)), ptr(ctx.err),
+        ctx.stream,
     )
     return out
 
@@ -458,6 +485,7 @@ def paged_flash_attention(
     max_q_len: int,
     splits: int = 1,
     value_head: int = -1,
+    shape: ScoreShape = NO_SHAPE,
 ) -> torch.Tensor:
     """Tensor-core attention for requests ``first_seq .. first_seq + num_seqs`` of the step. With ``value_head`` >= 0
     every query head's weights are applied to the values of that kv head (the cp.async kernel only). With
@@ -481,7 +509,7 @@ def paged_flash_attention(
     # slow to place. The TMA kernel always goes through scratch unless told otherwise: at
     # batch 1 both forms take 1.10 ms per step (the cp.async kernel 1.15), at batch 2 scratch
     # 1.10 and the cluster 1.12, from batch 4 on the cluster loses.
-    use_tma = decode and value_head == -1 and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+    use_tma = decode and value_head == -1 and not shape and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
     merge = ctx.options.get("attention_merge", "auto")
     if merge == "auto":
         merge = "cluster" if num_seqs * kv_heads * planes <= 4 and not use_tma else "scratch"
@@ -505,7 +533,7 @@ def paged_flash_attention(
         ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs),
         c_int(num_seqs if decode else ctx.num_tokens), c_int(max_q_len), c_int(cache.max_pages), c_int(cache.num_pages),
         c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale),
-        c_int(1 if decode else 0), c_int(splits), c_int(value_head), ptr(scratch), ptr(ctx.err), ctx.stream,
+        c_int(1 if decode else 0), c_int(splits), c_int(value_head), *shape.arguments(q_heads), ptr(scratch), ptr(ctx.err), ctx.stream,
     )
     if scratch is not None:
         ctx.lib.calls += 1  # the merge kernel is a launch of its own
@@ -670,16 +698,24 @@ def linear_per_head(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out
 
 def latent_kv_write(
     ctx: StepContext, cache: CacheView, proj: torch.Tensor, q_offset: int, kv_offset: int, heads: int, dim: int, rot_dim: int,
-    rank: int, norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, q_rot: torch.Tensor,
+    rank: int, norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, q_rot: torch.Tensor, *, q_proj: torch.Tensor | None = None,
+    halves: bool = False, magnitude: float = 1.0,
 ) -> None:
+    """``q_proj``: the matrix that holds the queries when it is not ``proj`` itself (queries that come out of a latent of
+    their own); ``halves``: number i of a rotated part pairs with i + half instead of 2i with 2i + 1; ``magnitude``
+    multiplies sine and cosine."""
     tokens, ld = proj.shape
+    queries = proj if q_proj is None else q_proj
+    _need(queries.is_contiguous() and queries.dtype == proj.dtype and queries.shape[0] == tokens and queries.shape[1] >= q_offset + heads * (dim + rot_dim),
+          "latent_kv_write: bad queries")
     _need(proj.is_contiguous() and cache.keys.dtype == proj.dtype and q_rot.dtype == proj.dtype, "latent_kv_write: bad operands")
     _need(tuple(q_rot.shape) == (tokens, heads * rot_dim) and q_rot.is_contiguous(), "latent_kv_write: bad q_rot")
     _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == rank and inv_freq.dtype == torch.float32, "latent_kv_write: bad constants")
     _need(tuple(cache.keys.shape[1:]) == (1, cache.page_size, rank + rot_dim), "latent_kv_write: the cache rows are [latent | rotated key part]")
     ctx.lib.call(
-        "b200_latent_kv_write", ptr(proj), c_int(ld), c_int(q_offset), c_int(kv_offset), c_int(tokens), c_int(heads), c_int(dim),
-        c_int(rot_dim), c_int(rank), ptr(norm_weight), c_float(eps), ptr(inv_freq), c_int(2 * inv_freq.numel()),
+        "b200_latent_kv_write", ptr(queries), c_int(queries.shape[1]), ptr(proj), c_int(ld), c_int(q_offset), c_int(kv_offset), c_int(tokens),
+        c_int(heads), c_int(dim), c_int(rot_dim), c_int(rank), ptr(norm_weight), c_float(eps), ptr(inv_freq), c_int(2 * inv_freq.numel()),
+        c_int(1 if halves else 0), c_float(magnitude),
         ptr(ctx.positions), ptr(ctx.token_seq), ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
         ptr(cache.keys), c_int(cache.page_size), c_int(1 if cache.writes else 0), ptr(q_rot), c_int(dtype_code(proj.dtype)),
         ptr(ctx.err), ctx.stream,
@@ -984,13 +1020,18 @@ def head_gate(ctx: StepContext, attn: torch.Tensor, proj: torch.Tensor | None, g
 # -- the routed feed-forward --------------------------------------------------------------------------------
 
 
-def moe_route(ctx: StepContext, logits: torch.Tensor, groups: int, keep: int, top: int, scale: float, ids: torch.Tensor, weights: torch.Tensor) -> None:
+def moe_route(ctx: StepContext, logits: torch.Tensor, groups: int, keep: int, top: int, scale: float, ids: torch.Tensor, weights: torch.Tensor,
+              *, bias: torch.Tensor | None = None, softmax_chosen: bool = False) -> None:
+    """``bias`` (float32 ``[experts]``) is added to the logits first. ``softmax_chosen``: an expert's score is its logit
+    and the chosen experts' weights are the softmax over their logits alone (times ``scale``); otherwise the score is
+    the logit's sigmoid and the weights are the chosen scores over their sum."""
     tokens, experts = logits.shape
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == experts and bias.is_contiguous()), "moe_route: the bias is float32 [experts]")
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: router logits are contiguous float32")
     _need(ids.dtype == torch.int32 and tuple(ids.shape) == (tokens, top) and ids.is_contiguous(), "moe_route: bad ids")
     _need(weights.dtype == torch.float32 and tuple(weights.shape) == (tokens, top) and weights.is_contiguous(), "moe_route: bad weights")
     ctx.lib.call(
-        "b200_moe_route", ptr(logits), c_int(tokens), c_int(experts), c_int(groups), c_int(keep), c_int(top), c_float(scale), ptr(ids),
+        "b200_moe_route", ptr(logits), ptr(bias), c_int(1 if softmax_chosen else 0), c_int(tokens), c_int(experts), c_int(groups), c_int(keep), c_int(top), c_float(scale), ptr(ids),
         ptr(weights), ctx.stream,
     )
 
@@ -1069,7 +1110,8 @@ def moe_combine(ctx: StepContext, expert_out: torch.Tensor, weights: torch.Tenso
 
 def clamped_glu(ctx: StepContext, gate_up: torch.Tensor, limit: float, out: torch.Tensor) -> torch.Tensor:
     """``out = g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``; rows of
-    ``gate_up`` are ``[gate | up]``."""
+    ``gate_up`` are ``[gate | up]``. A ``limit`` of zero is the unclamped form ``silu(gate) * up``, for the experts'
+    products (``moe_experts``) as well."""
     rows, twice = gate_up.shape
     ff = twice // 2
     _need(twice == 2 * ff and tuple(out.shape) == (rows, ff) and gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "clamped_glu: bad operands")
@@ -1234,3 +1276,102 @@ def embedding_bigram(
     )
     ctx.lib.calls += 1  # the slot update is a launch of its own
     return out
+
+
+# -- layer norm, the embedding that ends in one, and the row kernels of layers built around them ----------------------
+
+
+@dataclass
+class BranchSum:
+    """The outputs of two sublayers that read the same normed rows and are both still to be added to the stream
+    (``b`` may be None): the norm kernel that runs next adds them in 32-bit."""
+
+    a: torch.Tensor
+    b: torch.Tensor | None
+
+
+def layernorm(ctx: StepContext, x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``v = x + delta`` (a tensor, a :class:`BranchSum` or None; written back into ``x`` unless ``rows`` is given), ``out
+    = (v - mean) / sqrt(mean((v - mean)^2) + eps) * weight``."""
+    hidden = x.shape[1]
+    count = x.shape[0] if rows is None else rows.shape[0]
+    a, b = (delta.a, delta.b) if isinstance(delta, BranchSum) else (delta, None)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "layernorm: the residual stream is contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "layernorm: weight must be float32 [hidden]")
+    _need(tuple(out.shape) == (count, hidden) and out.is_contiguous(), "layernorm: bad output shape")
+    for d in (a, b):
+        _need(d is None or (d.shape == x.shape and d.dtype == out.dtype and d.is_contiguous()), "layernorm: bad pending branch output")
+    ctx.lib.call(
+        "b200_layernorm", ptr(x), ptr(a), ptr(b), ptr(weight), ptr(rows), c_int(count), c_int(hidden), c_float(eps), ptr(out),
+        c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def embedding_layernorm(ctx: StepContext, table: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = layer norm of table[token[t]]`` in 32-bit."""
+    vocab, hidden = table.shape
+    _need(tuple(out.shape) == (ctx.num_tokens, hidden) and out.dtype == torch.float32, "embedding: bad output")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "embedding: the norm's weight is float32 [hidden]")
+    ctx.lib.call(
+        "b200_embedding_layernorm", ptr(table), ptr(ctx.token_ids), ptr(weight), c_float(eps), ptr(out), c_int(ctx.num_tokens), c_int(hidden),
+        c_int(vocab), c_int(dtype_code(table.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+def rms_rows(ctx: StepContext, rows_in: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """``out = v / sqrt(mean(v^2) + eps) * weight`` per row of ``rows_in`` (a view with any row stride)."""
+    count, width = rows_in.shape
+    _need(rows_in.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (count, width) and out.dtype == rows_in.dtype, "rms_rows: bad operands")
+    _need(weight.dtype == torch.float32 and weight.numel() == width, "rms_rows: weight must be float32 [width]")
+    ctx.lib.call(
+        "b200_rms_rows", ptr(rows_in), c_int64(rows_in.stride(0)), ptr(weight), c_float(eps), c_int(count), c_int(width), ptr(out),
+        c_int64(out.stride(0)), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def sigmoid_mul(ctx: StepContext, a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = a * sigmoid(gate)`` element by element; ``gate`` may be a view of wider rows."""
+    rows, width = a.shape
+    _need(a.is_contiguous() and out.is_contiguous() and out.shape == a.shape and out.dtype == a.dtype, "sigmoid_mul: bad operands")
+    _need(tuple(gate.shape) == (rows, width) and gate.stride(1) == 1 and gate.dtype == a.dtype, "sigmoid_mul: bad gate")
+    ctx.lib.call("b200_sigmoid_mul", ptr(a), ptr(gate), c_int64(gate.stride(0)), c_int(rows), c_int(width), ptr(out), c_int(dtype_code(a.dtype)), ctx.stream)
+    return out
+
+
+def scale_values(ctx: StepContext, values: torch.Tensor, scale: float) -> torch.Tensor:
+    _need(values.dtype == torch.float32 and values.is_contiguous(), "scale_values: contiguous float32")
+    ctx.lib.call("b200_scale_values", ptr(values), c_int64(values.numel()), c_float(scale), ctx.stream)
+    return values
+
+
+def qk_norm_rope_write(
+    ctx: StepContext, cache: CacheView, proj: torch.Tensor, bias: torch.Tensor | None, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+    eps: float, inv_freq: torch.Tensor | None, magnitude: float, values_from_keys: bool, q_out: torch.Tensor, q_heads: int, kv_heads: int,
+    dim: int, vdim: int, row_dim: int,
+) -> torch.Tensor:
+    """Per token of ``proj`` (rows ``[q | k | v | ...]``, no v part with ``values_from_keys``): bias; one RMS norm over all of
+    q and one over all of k (``q_weight`` / ``k_weight``; None: no norm); the first ``2 * len(inv_freq)`` numbers of every
+    head rotated in halves by ``position * inv_freq``, sine and cosine times ``magnitude``; queries to ``q_out``, keys and
+    values (the keys as projected, with ``values_from_keys``) to the token's page, rows padded to ``row_dim``."""
+    tokens, ld = proj.shape
+    width = (q_heads + kv_heads) * dim + (0 if values_from_keys else kv_heads * vdim)
+    rot_dims = 2 * inv_freq.numel() if inv_freq is not None else 0
+    _need(proj.is_contiguous() and cache.keys.dtype == proj.dtype and cache.values is not None, "qk_norm_rope_write: bad operands")
+    _need(tuple(q_out.shape) == (tokens, q_heads * row_dim) and q_out.is_contiguous() and q_out.dtype == proj.dtype, "qk_norm_rope_write: bad q_out")
+    _need(tuple(cache.keys.shape[1:]) == (kv_heads, cache.page_size, row_dim), "qk_norm_rope_write: the cache rows differ from the padded head size")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "qk_norm_rope_write: the bias is float32 over q, k (and v)")
+    _need(q_weight is None or (q_weight.dtype == torch.float32 and q_weight.numel() == q_heads * dim), "qk_norm_rope_write: bad q weight")
+    _need(k_weight is None or (k_weight.dtype == torch.float32 and k_weight.numel() == kv_heads * dim), "qk_norm_rope_write: bad k weight")
+    _need(inv_freq is None or inv_freq.dtype == torch.float32, "qk_norm_rope_write: bad frequency table")
+    ctx.lib.call(
+        "b200_qk_norm_rope_write", ptr(proj), c_int(ld), ptr(bias), ptr(q_weight), ptr(k_weight), c_float(eps), ptr(inv_freq), c_int(rot_dims),
+        c_float(magnitude), c_int(1 if values_from_keys else 0), ptr(ctx.positions), ptr(ctx.token_seq), ptr(ctx.seq_kv_len), ptr(cache.block_table),
+        c_int(cache.max_pages), c_int(cache.num_pages), ptr(cache.keys), ptr(cache.values), ptr(q_out), c_int(tokens), c_int(q_heads),
+        c_int(kv_heads), c_int(dim), c_int(vdim), c_int(row_dim), c_int(cache.page_size), c_int(1 if cache.writes else 0),
+        c_int(dtype_code(proj.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return q_out
