@@ -57,7 +57,26 @@ def _lerorax(width, vocab, blocks, heads, kv_heads, ff, shared=False):
     }
 
 
+def _zetizen(width, vocab, blocks, heads, kv_heads, experts, top, ff):
+    """``blocks`` triples of (attention with a bias by distance, chunked attention whose values are its keys, attention
+    over latents), each beside a routed feed-forward with a shared expert."""
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": 2 * ff}, "router": {"experts": experts, "top": top}}
+    ramp = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    biased = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "bias_max": 512, "bias_rows": 32}}
+    chunked = {"type": "attention_2", "mlp": mlp, "mixer": {
+        "heads": heads // 2, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024},
+        "rot": {"dims": 64, "base": 1e6, "scaling": ramp}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "scale": 96 ** -0.5,
+        "rot": {"dims": 32, "base": 1e4, "scaling": ramp}}}
+    return {"architecture": "Zetizen", "vocab": vocab, "width": width, "logit_scale": 0.25, "norm": {"eps": 1e-5},
+            "layers": [biased, chunked, latent] * blocks}
+
+
 PRESETS = {
+    "zetizen-small": _zetizen(512, 8192, 2, 8, 2, 16, 2, 256),
+    "zetizen-1b": _zetizen(2048, 32768, 4, 16, 4, 16, 2, 512),
     "lerorax-small": _lerorax(512, 8192, 2, 4, 2, 1024, shared=True),
     "lerorax-1b": _lerorax(2048, 32768, 6, 16, 4, 5632),
     "tunadra-small": _tunadra(512, 8192, 3, 8, 2, 16, 2, 256),

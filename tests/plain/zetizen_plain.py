@@ -127,19 +127,21 @@ def _grow(state: dict, name: str, rows: np.ndarray) -> np.ndarray:
 
 
 def biased_attention(h: np.ndarray, w: dict, p: str, m: dict, eps: float, positions, state: dict) -> np.ndarray:
-    """Grouped-query attention without rotation: one RMS norm over all of q and one over all of k, capped scores,
-    a learned bias by distance."""
+    """Grouped-query attention without rotation: one RMS norm over all of q and one over all of k, capped scores
+    (with ``softcap``), a learned bias by distance (with ``bias_max``)."""
     heads, groups, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     t_count = h.shape[0]
     q = rms_norm(linear(h, w[p + "q"]), w[p + "q.norm"], eps).reshape(t_count, heads, dim)
     k = rms_norm(linear(h, w[p + "k"]), w[p + "k.norm"], eps).reshape(t_count, groups, dim)
     v = linear(h, w[p + "v"]).reshape(t_count, groups, vdim)
     keys, values = _grow(state, "k", k), _grow(state, "v", v)
-    table = w[p + "rel"].astype(F64)
-    rows = table.shape[0]
+    bias = None
+    if m.get("bias_max"):
+        table = w[p + "rel"].astype(F64)
+        rows = table.shape[0]
 
-    def bias(distance: int, head: int) -> float:
-        return table[distance_bucket(distance, rows, m["bias_max"]), head]
+        def bias(distance: int, head: int) -> float:
+            return table[distance_bucket(distance, rows, m["bias_max"]), head]
 
     out = attend(q, keys, values, positions, m["scale"], m.get("softcap"), bias)
     return linear(out.reshape(t_count, heads * vdim), w[p + "o"])
@@ -205,16 +207,18 @@ def route(logits: np.ndarray, top: int) -> tuple[np.ndarray, np.ndarray]:
     return order, softmax(np.take_along_axis(logits, order, axis=-1))
 
 
-def routed_experts(h: np.ndarray, w: dict, p: str, mlp: dict, choices=None, margins=None) -> np.ndarray:
+def routed_experts(h: np.ndarray, w: dict, p: str, mlp: dict, choices=None, margins=None, free=None) -> np.ndarray:
     """``choices`` (``[T, top]`` expert ids) replaces the router's own choice of experts (their weights are still the
-    softmax over the chosen logits); ``margins`` (a list) receives, per token, the gap between the last chosen and the
-    first rejected logit."""
+    softmax over the chosen logits); ``margins`` (a list) receives one array per call, per token the gap between the
+    last chosen and the first rejected logit, and ``free`` (a list) the router's own choices."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
     logits = linear(h, w[p + "router"], w[p + "router.b"])
     ids, weights = route(logits, top)
     if margins is not None:
         ordered = -np.sort(-logits, axis=-1)
-        margins.extend((ordered[:, top - 1] - ordered[:, top]).tolist() if top < experts else [np.inf] * h.shape[0])
+        margins.append(ordered[:, top - 1] - ordered[:, top] if top < experts else np.full(h.shape[0], np.inf))
+    if free is not None:
+        free.append(ids.copy())
     if choices is not None:
         ids = np.asarray(choices, dtype=np.int64)
         weights = softmax(np.take_along_axis(logits, ids, axis=-1))
@@ -235,10 +239,11 @@ def new_state(config: dict) -> dict:
 
 
 def forward(config: dict, weights: dict, tokens, state: dict | None = None, *, layer_outputs: list | None = None,
-            choices: dict | None = None, margins: list | None = None) -> tuple[np.ndarray, dict]:
+            choices: dict | None = None, margins: list | None = None, free: list | None = None) -> tuple[np.ndarray, dict]:
     """Feed ``tokens`` (the next ones of the sequence ``state`` belongs to; None: a new sequence). Returns the logits
     ``[T, vocab]`` and the state. ``layer_outputs`` receives the stream after every layer; ``choices`` maps a layer index
-    to the experts to use (``[T, top]``)."""
+    to the experts to use (``[T, top]``); ``margins`` and ``free`` receive one entry per routed layer (see
+    :func:`routed_experts`)."""
     state = new_state(config) if state is None else state
     eps = config["norm"]["eps"]
     tokens = np.asarray(tokens, dtype=np.int64)
@@ -251,9 +256,19 @@ def forward(config: dict, weights: dict, tokens, state: dict | None = None, *, l
         h = layer_norm(x, weights[p + "norm1"], eps)
         branch = MIXERS[layer["type"]](h, weights, p + "mix.", layer["mixer"], eps, positions, state["layers"][index])
         if layer.get("mlp") is not None:
-            branch = branch + routed_experts(h, weights, p + "mlp.", layer["mlp"], None if choices is None else choices.get(index), margins)
+            branch = branch + routed_experts(h, weights, p + "mlp.", layer["mlp"], None if choices is None else choices.get(index), margins, free)
         x = x + branch
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
     logits = linear(layer_norm(x, weights["final.norm"], eps), table) * config["logit_scale"]
     return logits, state
+
+
+def greedy(config: dict, weights: dict, prompt, count: int) -> list[int]:
+    """``count`` tokens, each the arg-max of the last position's logits, fed back one by one."""
+    logits, state = forward(config, weights, prompt)
+    out = []
+    for _ in range(count):
+        out.append(int(np.argmax(logits[-1])))
+        logits, state = forward(config, weights, [out[-1]], state)
+    return out
