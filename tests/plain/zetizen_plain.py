@@ -260,7 +260,7 @@ def forward(config: dict, weights: dict, tokens, state: dict | None = None, *, l
         x = x + branch
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
-    logits = linear(layer_norm(x, weights["final.norm"], eps), table) * config["logit_scale"]
+    logits = linear(layer_norm(x, weights["final.norm"], eps), table) * config.get("logit_scale", 1.0)
     return logits, state
 
 

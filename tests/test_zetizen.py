@@ -292,7 +292,8 @@ def test_latent_attention_with_a_query_latent_alone_in_portions(name, case):
     long = inputs[10].double().numpy()
     assert np.abs(expect(long, table=dict(w64, **{"l0.mix.g": 0 * w64["l0.mix.g"]})) - want[10]).max() > 0.05
     assert np.abs(expect(long, table=dict(w64, **{"l0.mix.dq.norm": np.roll(w64["l0.mix.dq.norm"], 1)})) - want[10]).max() > 0.01
-    assert np.abs(expect(long, dict(m, rot=dict(m["rot"], base=m["rot"]["base"] * 7))) - want[10]).max() > 0.005
+    if m["rot_dim"] > 2:  # a rotated part of two numbers has the one frequency 1, whatever the base
+        assert np.abs(expect(long, dict(m, rot=dict(m["rot"], base=m["rot"]["base"] * 7))) - want[10]).max() > 0.005
     got = run_in_portions(mixer, weights, dtype, inputs, total)
     np.testing.assert_allclose(got[10], want[10], **CLOSE[name])
     np.testing.assert_allclose(got[11], want[11], **CLOSE[name])
