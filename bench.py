@@ -334,7 +334,30 @@ def lerorax_shape(width: int) -> dict:
     }
 
 
-DESIGN_SHAPES = {"gunedra": gunedra_shape, "tunadra": tunadra_shape, "lerorax": lerorax_shape}
+def zetizen_shape(width: int) -> dict:
+    """Layer sizes in the proportions of a real model of this design: attention heads of 128 sharing key/value heads as
+    the Qwen2 shape does, one kind with a soft cap and a bias by distance (32 rows up to 1,024 positions), one whose
+    values are its keys, half rotated, in chunks of 1,024 positions; attention over latents of 512 + 64 with queries out
+    of a latent of 1,536; and the routed feed-forward of the Tunadra shape of this width (32 experts, four per token, a
+    shared expert) without groups or clamps."""
+    heads, ff = DESIGN_SIZES[width]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 2}, "router": {"experts": 32, "top": 4}}
+    ramp = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    kv_heads = max(1, heads // 6)
+    biased = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "bias_max": 1024, "bias_rows": 32}}
+    chunked = {"type": "attention_2", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024},
+        "rot": {"dims": 64, "base": 1e6, "scaling": ramp}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "scale": 192 ** -0.5,
+        "rot": {"dims": 64, "base": 1e6, "scaling": ramp}}}
+    return {"architecture": "Zetizen", "vocab": DESIGN_VOCAB, "width": width, "logit_scale": 0.25, "norm": {"eps": 1e-5},
+            "layers": [biased, chunked, latent, biased][:DESIGN_LAYERS]}
+
+
+DESIGN_SHAPES = {"gunedra": gunedra_shape, "tunadra": tunadra_shape, "lerorax": lerorax_shape, "zetizen": zetizen_shape}
+CLOSEST = {"lerorax": "gunedra", "zetizen": "tunadra"}  # the existing design each is put beside by default (others: the Qwen2 shape)
 # The design each is put beside: the Qwen2 shape of equal width, or (--beside) another design's shape of equal width.
 
 
@@ -369,7 +392,7 @@ def compare_designs(args) -> int:
     batch = args.batch
     results = {}
     for width in [int(w) for w in args.design_sizes.split(",")]:
-        beside = args.beside or ("gunedra" if args.design == "lerorax" else "qwen2")
+        beside = args.beside or CLOSEST.get(args.design, "qwen2")
         other = qwen2_shape(width) if beside == "qwen2" else DESIGN_SHAPES[beside](width)
         for design, raw in ((args.design, DESIGN_SHAPES[args.design](width)), (beside, other)):
             _, config = parse_config(raw)
@@ -509,10 +532,11 @@ def main() -> int:
                         help="instead of the headline run: prefill and decode of another design (--design) beside the Qwen2 shape of "
                         "equal width, feed-forward and head count, at a few layer sizes, with each kernel's time")
     parser.add_argument("--design-sizes", default="1536,3584", help="widths for --designs (1536, 3584 or 5120)")
-    parser.add_argument("--design", choices=["gunedra", "tunadra", "lerorax"], default="gunedra", help="which design --designs puts beside the Qwen2 shape")
+    parser.add_argument("--design", choices=["gunedra", "tunadra", "lerorax", "zetizen"], default="gunedra", help="which design --designs puts beside the Qwen2 shape")
     parser.add_argument("--beside", choices=["qwen2", "gunedra", "tunadra"], default=None,
                         help="--designs: the shape of equal width to put the design beside (default: qwen2; for lerorax gunedra, the "
-                        "closest design: blocks that norm their branches' outputs, a delta rule, short convolutions, a dense feed-forward)")
+                        "closest design: blocks that norm their branches' outputs, a delta rule, short convolutions, a dense feed-forward; for "
+                        "zetizen tunadra: attention mixers over the paged cache beside a routed feed-forward with a shared expert)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -16,7 +16,7 @@ namespace {
 
 template <typename T>
 __global__ void layernorm_kernel(float* x, const T* delta_a, const T* delta_b, const float* __restrict__ weight,
-                                 const int* __restrict__ rows, int hidden, float eps, T* out) {
+                                 const int* rows, int hidden, float eps, T* out) {
   extern __shared__ float ln_row[];
   __shared__ float scratch[32];
   wait_for_predecessor();
@@ -48,7 +48,7 @@ __global__ void layernorm_kernel(float* x, const T* delta_a, const T* delta_b, c
 }
 
 template <typename T>
-__global__ void embedding_layernorm_kernel(const T* __restrict__ table, const int* __restrict__ ids, const float* __restrict__ weight,
+__global__ void embedding_layernorm_kernel(const T* __restrict__ table, const int* ids, const float* __restrict__ weight,
                                            float eps, float* x, int hidden, int vocab, int* err) {
   extern __shared__ float ln_row[];
   __shared__ float scratch[32];
