@@ -188,7 +188,8 @@ def bench_gemm(args) -> dict:
 def bench_attention(args, decode: bool, mixed: bool = False) -> dict:
     """``mixed``: attention whose softmax weights are mixed over heads (parts/mixed_attention.py): one pass per kv
     head, every query head's weights applied to that head's values, then the kernel that mixes and gates. Its
-    flops count what the passes execute (``kv_heads`` times the scores and the weighted sums of all query heads)."""
+    flops count what the passes execute (``kv_heads`` times the scores and the weighted sums of all query heads).
+    ``--softcap``, ``--bias-reach`` and ``--chunk`` shape the scores (``ops.ScoreShape``); flops then count the visible keys."""
     from ..parts import attention_dispatch, ops
     from ..parts.context import CacheView
 
@@ -235,15 +236,18 @@ def bench_attention(args, decode: bool, mixed: bool = False) -> dict:
 
             fns.append(passes)
             continue
-        fns.append(lambda view=view: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5))
+        shape = ops.ScoreShape(args.softcap, torch.randn(q_heads, args.bias_reach + 1, device="cuda") if args.bias_reach else None, args.chunk)
+        fns.append(lambda view=view, shape=shape: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5, shape=shape))
     # --rotate: back to back inside a CUDA graph, so that neither the host's launch cost nor
     # the idle gap before a lone launch enters (with one arena the cache stays in L2, as it
     # does in a small model's step, where the layer's keys were written just before).
     us = time_back_to_back(fns, 16 * len(fns)) if args.rotate else time_launches(fns[0], args.iters)
     kv_bytes = sum(lens) * kv_heads * dim * 2 * 2
     flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs)) * (kv_heads if mixed else 1)
+    if args.chunk and not mixed:
+        flops = sum(4.0 * q_heads * dim * (p % args.chunk + 1) for p in positions)
     return {"kernel": ("mixed_" if mixed else "") + ("decode_attention" if decode else "prefill_attention"), "batch": len(lens), "context": args.context,
-            "tokens": len(positions), "loader": args.loader, "splits": args.splits, "stages": args.stages,
+            "tokens": len(positions), "softcap": args.softcap, "bias_reach": args.bias_reach, "chunk": args.chunk, "loader": args.loader, "splits": args.splits, "stages": args.stages,
             "layers": args.layers, "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
 
@@ -536,6 +540,9 @@ def main(argv=None) -> int:
     parser.add_argument("--page", type=int, default=64)
     parser.add_argument("--window", type=int, default=0)
     parser.add_argument("--plain", action="store_true")
+    parser.add_argument("--softcap", type=float, default=0.0, help="attention: cap of the scores (0: none)")
+    parser.add_argument("--bias-reach", type=int, default=0, help="attention: a random bias by distance up to this many positions (0: none)")
+    parser.add_argument("--chunk", type=int, default=0, help="attention: keys visible inside the query's chunk of this many positions (0: all)")
     parser.add_argument("--attention", default="auto", choices=["auto", "flash", "tcgen05"])
     parser.add_argument("--loader", default="auto", choices=["auto", "tma", "cp_async"], help="how decode attention loads keys and values")
     parser.add_argument("--splits", type=int, default=0, help="blocks per (request, kv head) in decode attention (0: the engine's rule)")

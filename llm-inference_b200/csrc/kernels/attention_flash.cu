@@ -62,8 +62,25 @@ struct FlashParams {
                       // one launch; value head c's results lie c * plane_tokens token rows further in `out` and in scratch
   float scale_log2;
   float scale;       // the shaped form caps and biases the scaled score before it goes to base 2
+  float cap_twice_inv;  // 2 / softcap
   ScoreShape shape;  // soft cap, bias by distance, chunk of visible keys (the SHAPED instantiations only)
 };
+
+// The shaped score of the bfloat16 kernels, in base 2 (what the running softmax works in). cap * tanh(x / cap) is
+// formed as cap * (1 - 2 / (exp(2 x / cap) + 1)) with the fast exponential and division: two special-function
+// operations and an absolute error of about 1e-6 * cap, far below what bfloat16 operands leave in a score (the
+// 32-bit path runs the plain kernel, which calls tanhf). `raw` is the unscaled q . k; the bias row is read at
+// min(max(distance, 0), reach), so rows and keys that the mask removes afterwards read inside the table.
+__device__ __forceinline__ float shaped_score_fast(float raw, const FlashParams& p, const float* bias_row, int distance, bool far,
+                                                   float far_bias) {
+  float s = raw * p.scale;
+  if (p.shape.softcap > 0.f) {
+    const float t = __expf(s * p.cap_twice_inv);
+    s = p.shape.softcap - __fdividef(2.f * p.shape.softcap, t + 1.f);
+  }
+  if (bias_row != nullptr) s += far ? far_bias : __ldg(bias_row + min(max(distance, 0), p.shape.bias_reach));
+  return s * kLog2e;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -393,6 +410,7 @@ paged_flash_attention_kernel(const FlashParams p) {
   const int chunk_lo0 = SHAPED && chunk > 0 ? pos0 / chunk * chunk : 0, chunk_lo1 = SHAPED && chunk > 0 ? pos1 / chunk * chunk : 0;
   const float* bias0 = SHAPED && p.shape.bias ? p.shape.bias + static_cast<int64_t>(head0) * (p.shape.bias_reach + 1) : nullptr;
   const float* bias1 = SHAPED && p.shape.bias ? p.shape.bias + static_cast<int64_t>(head1) * (p.shape.bias_reach + 1) : nullptr;
+  const float far_bias0 = bias0 ? __ldg(bias0 + p.shape.bias_reach) : 0.f, far_bias1 = bias1 ? __ldg(bias1 + p.shape.bias_reach) : 0.f;
 
   float o[kDimTiles][4];
 #pragma unroll
@@ -451,6 +469,8 @@ paged_flash_attention_kernel(const FlashParams p) {
         (tile_start + kTileKeys - 1 > first_pos + min(tok0, q_len - 1)) ||
         (p.window > 0 && tile_start <= pos1 - p.window) || (tile_start < lo) || !live1 || (SHAPED && chunk > 0);
 
+    // Every key of the tile at or beyond the bias's reach from every row of the warp: one number per row serves.
+    const bool far_tile = SHAPED && bias0 != nullptr && __all_sync(0xffffffffu, pos0 - (tile_start + kTileKeys - 1) >= p.shape.bias_reach);
     {
       // A prefill warp takes all 64 keys of the tile for its 16 rows (eight independent score
       // tiles, one softmax update per tile); a decode warp takes its quarter of the tile.
@@ -484,8 +504,7 @@ paged_flash_attention_kernel(const FlashParams p) {
           float v = s[n][e] * p.scale_log2;
           const int key = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
           const int pos = e < 2 ? pos0 : pos1;
-          if (SHAPED)
-            v = shaped_score(s[n][e] * p.scale, p.shape, e < 2 ? bias0 : bias1, max(pos - key, 0)) * kLog2e;
+          if (SHAPED) v = shaped_score_fast(s[n][e], p, e < 2 ? bias0 : bias1, pos - key, far_tile, e < 2 ? far_bias0 : far_bias1);
           if (tile_needs_mask) {
             const bool live = e < 2 ? live0 : live1;
             const bool visible = live && key <= pos && key >= lo && (p.window == 0 || key > pos - p.window) &&
@@ -1112,6 +1131,7 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
   p.scale_log2 = scale * kLog2e;
   p.scale = scale;
   p.shape = ScoreShape{softcap, bias, bias_reach, chunk};
+  p.cap_twice_inv = softcap > 0.f ? 2.f / softcap : 0.f;
   p.err = err;
   p.partial_out = scratch;
   const int64_t planes = every_value_head ? kv_heads : 1;
@@ -1183,6 +1203,7 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   p.scale_log2 = scale * kLog2e;
   p.scale = scale;
   p.shape = ScoreShape{0.f, nullptr, 0, 0};
+  p.cap_twice_inv = 0.f;
   p.err = err;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<int64_t>(num_seqs) * q_heads * splits * head_dim : nullptr;

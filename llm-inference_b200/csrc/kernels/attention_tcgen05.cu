@@ -57,6 +57,9 @@ struct PrefillParams {
   int window;
   int value_head;  // >= 0: every block takes its values from this kv head's rows of the pages (keys stay its own)
   float scale_log2;
+  // The capped form only: scores pass cap * tanh(score / cap) and a query sees only the keys of its own chunk.
+  float scale, softcap, cap_twice_inv;  // cap_twice_inv = 2 / softcap (0: no cap)
+  int chunk;                            // > 0: keys visible from floor(pos / chunk) * chunk on
 };
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -186,6 +189,21 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// A raw score q . k as the exponent (base 2) the softmax works with: scale, the soft cap formed as
+// cap * (1 - 2 / (exp(2 s / cap) + 1)) with the fast exponential and division (two special-function operations, an
+// absolute error of about 1e-6 * cap), then log2(e). A masked score (-inf) stays -inf.
+__device__ __forceinline__ float capped_exponent(float raw, const PrefillParams& p) {
+  float s = raw * p.scale;
+  if (p.softcap > 0.f) {
+    const float t = __expf(s * p.cap_twice_inv);
+    s = p.softcap - __fdividef(2.f * p.softcap, t + 1.f);
+  }
+  return raw == -INFINITY ? -INFINITY : s * kLog2eA;
+}
+
+// CAPPED: the scores are soft-capped and chunks bound the visible keys (PrefillParams); the plain instantiation carries
+// none of that code. The cap grows with the score, so a tile's maximum is still found on the raw scores.
+template <bool CAPPED>
 __global__ void __launch_bounds__(kThreadsA, 1)
 flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              const PrefillParams p) {
@@ -229,7 +247,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
 
   const int first_token = row_base / p.group;
   const int last_token = min(q_len - 1, (row_base + kRows - 1) / p.group);
-  const int lo = p.window > 0 ? max(0, first_pos + first_token - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, first_pos + first_token - p.window + 1) : 0;
+  if (CAPPED && p.chunk > 0) lo = max(lo, (first_pos + first_token) / p.chunk * p.chunk);  // the first row sees furthest back
   const int hi = first_pos + last_token;  // inclusive
   const int tile_begin = lo / kKeys, tile_end = hi / kKeys + 1;
   const int num_tiles = tile_end - tile_begin;
@@ -463,7 +482,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       const uint32_t s_addr = (tmem + (it % kScoreBuffers) * 128) + lane_addr;
       // Keys [rel_lo, rel_hi] of this tile are the ones this row attends to.
       const int rel_hi = live ? pos - tile_start : -1;
-      const int rel_lo = p.window > 0 ? pos - p.window + 1 - tile_start : 0;
+      int rel_lo = p.window > 0 ? pos - p.window + 1 - tile_start : 0;
+      if (CAPPED && p.chunk > 0) rel_lo = max(rel_lo, pos / p.chunk * p.chunk - tile_start);
       const bool needs_mask = __any_sync(0xffffffffu, rel_hi < kKeys - 1 || rel_lo > 0);
       // Two passes over the scores, 32 columns at a time (rolled loops: fully unrolled, this code
       // outgrew the instruction cache and the warps starved on fetches). Pass 1: the maximum.
@@ -485,7 +505,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
           mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
         }
       }
-      const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float raw_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const float tile_max = CAPPED ? capped_exponent(raw_max, p) : raw_max * p.scale_log2;
       // The offset m is only moved when this tile's maximum exceeds it by more than kSlack (in
       // log2 units): probabilities may then be as large as 2^kSlack, which bfloat16 and the
       // 32-bit sums take easily, and in exchange most tiles need no rescaling of the running
@@ -542,10 +563,18 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -offset));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -offset));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -offset));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -offset));
+          float p0, p1, p2, p3;
+          if (CAPPED) {
+            p0 = fast_exp2(capped_exponent(__uint_as_float(raw[i]), p) - offset);
+            p1 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 1]), p) - offset);
+            p2 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 2]), p) - offset);
+            p3 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 3]), p) - offset);
+          } else {
+            p0 = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -offset));
+            p1 = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -offset));
+            p2 = fast_exp2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -offset));
+            p3 = fast_exp2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -offset));
+          }
           sum0 += p0;
           sum1 += p1;
           sum2 += p2;
@@ -656,9 +685,10 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
                                         const int* block_table, const int* seq_q_start, const int* seq_q_len,
                                         const int* seq_kv_len, int first_seq, int num_seqs, int max_q_len,
                                         int max_kv_len, int max_pages, int num_pages, int q_heads, int kv_heads,
-                                        int head_dim, int page_size, int window, float scale, int value_head, int* err,
-                                        cudaStream_t stream) {
+                                        int head_dim, int page_size, int window, float scale, int value_head, float softcap,
+                                        int chunk, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  B200_REQUIRE(softcap >= 0.f && chunk >= 0, "flash_prefill_tcgen05: bad cap or chunk");
   B200_REQUIRE(b200_flash_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_size, max_kv_len),
                "flash_prefill_tcgen05: unsupported shape (heads %d/%d, head_dim %d, page %d, %d keys)", q_heads, kv_heads,
                head_dim, page_size, max_kv_len);
@@ -686,6 +716,11 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   p.window = window;
   p.value_head = value_head;
   p.scale_log2 = scale * kLog2eA;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.cap_twice_inv = softcap > 0.f ? 2.f / softcap : 0.f;
+  p.chunk = chunk;
+  const bool capped = softcap > 0.f || chunk > 0;
   CUtensorMap k_map, v_map;
   const int64_t rows = static_cast<int64_t>(num_pages) * kv_heads * page_size;
   if (arena_map(&k_map, k_arena, rows, p.piece_rows) != 0) return -1;
@@ -693,7 +728,9 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   const size_t smem = (1 + kStagesK + kStagesV) * static_cast<size_t>(kTileBytesA) + kMaxChunks * sizeof(int) + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return b200_fail("flash_prefill_tcgen05: cannot size shared memory (%zu bytes)", smem);
     configured = true;
@@ -701,7 +738,8 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   const int row_blocks = (max_q_len * p.group + kRows - 1) / kRows;
   const dim3 grid(row_blocks, kv_heads, num_seqs);
   const cudaError_t status =
-      launch_kernel(flash_prefill_tcgen05_kernel, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p);
+      capped ? launch_kernel(flash_prefill_tcgen05_kernel<true>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p)
+             : launch_kernel(flash_prefill_tcgen05_kernel<false>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p);
   if (status != cudaSuccess) return b200_fail("flash_prefill_tcgen05: %s", cudaGetErrorString(status));
   return 0;
 }

@@ -31,8 +31,9 @@ def attend(
     shape: ops.ScoreShape = ops.NO_SHAPE,
 ) -> None:
     """``shape``: a soft cap, a bias by distance and a chunk of visible keys (``ops.ScoreShape``); the plain kernel and the
-    mma.sync kernels take it, so shaped attention of prompt portions runs the mma.sync prefill form and decoded tokens the
-    cp.async split-key kernel, whatever the head size.
+    mma.sync kernels take all of it, the tcgen05 prefill kernel the cap and the chunks. So prompt portions with a cap or
+    chunks run on tcgen05 where its sizes hold, those with a bias the mma.sync prefill form, and decoded tokens with any
+    shaping the cp.async split-key kernel.
 
     ``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
     instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head); the
@@ -62,12 +63,12 @@ def attend(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head, shape=shape,
         )
-    if ctx.num_seqs > decode_seqs and not shape and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+    if ctx.num_seqs > decode_seqs and shape.bias is None and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
         ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
     ):
         ops.paged_prefill_attention_tcgen05(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
-            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len, value_head=value_head,
+            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len, value_head=value_head, shape=shape,
         )
     elif ctx.num_seqs > decode_seqs:
         if choice == "tcgen05":

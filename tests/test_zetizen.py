@@ -301,8 +301,9 @@ def test_latent_attention_with_a_query_latent_alone_in_portions(name, case):
 
 @pytest.mark.parametrize("case", ["biased, heads of 64", "chunked, chunks of 21, heads of 128", "chunked, chunks of 8 (a page), heads of 64 rotated whole"])
 def test_tensor_core_kernels_against_the_plain_kernel_far_in(case):
-    """bfloat16, 600 keys: a prompt portion and single tokens at a page border and just past a chunk edge run the mma.sync
-    kernels (split keys for the single tokens) and the plain kernel; unwritten rows of the pages hold NaN."""
+    """bfloat16, 600 keys over pages of 16: prompt portions run the tcgen05 kernel (heads of 128 with a cap and chunks) or
+    the mma.sync prefill kernel, single tokens at a page border and just past a chunk edge the split-key kernel; the same
+    steps run the plain kernel. Unwritten rows of the pages hold NaN."""
     from llm_inference_b200.models.zetizen import zetizen_mixer
     from llm_inference_b200.parts import build_part
 
@@ -324,7 +325,7 @@ def test_tensor_core_kernels_against_the_plain_kernel_far_in(case):
         cache = PagedCache({0: mixer.cache_spec()}, dtype=torch.bfloat16, device=device, page_size=16, max_num_sequences=4, max_model_length=1024,
                            step_tokens=1024, num_pages=64)
         for group in cache.groups:
-            group.arena.fill_(float("nan"))
+            group.arena[:, :, :-1].fill_(float("nan"))  # every page a request can hold; the spare page that pads block tables stays finite
         runner = ModelRunner(SimpleNamespace(device=device, dtype=torch.bfloat16), cache, max_batch_tokens=1024, options={"attention": choice})
         mixer.load(weights, torch.bfloat16, device)
         cache.open(10)
