@@ -236,7 +236,8 @@ def bench_attention(args, decode: bool, mixed: bool = False) -> dict:
 
             fns.append(passes)
             continue
-        shape = ops.ScoreShape(args.softcap, torch.randn(q_heads, args.bias_reach + 1, device="cuda") if args.bias_reach else None, args.chunk)
+        bias = torch.randn(q_heads, args.bias_reach + 1, device="cuda") if args.bias_reach else None
+        shape = ops.ScoreShape(args.softcap, bias, args.chunk, bias.max(dim=1).values.contiguous() if bias is not None else None)
         fns.append(lambda view=view, shape=shape: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5, shape=shape))
     # --rotate: back to back inside a CUDA graph, so that neither the host's launch cost nor
     # the idle gap before a lone launch enters (with one arena the cache stays in L2, as it

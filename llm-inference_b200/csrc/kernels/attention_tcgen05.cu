@@ -60,6 +60,9 @@ struct PrefillParams {
   // The capped form only: scores pass cap * tanh(score / cap) and a query sees only the keys of its own chunk.
   float scale, softcap, cap_twice_inv;  // cap_twice_inv = 2 / softcap (0: no cap)
   int chunk;                            // > 0: keys visible from floor(pos / chunk) * chunk on
+  const float* bias;       // [q_heads][bias_reach + 1] by distance min(pos - key, bias_reach), added after the cap; null: none
+  const float* bias_peak;  // [q_heads]: the largest entry of the head's row
+  int bias_reach;
 };
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -201,9 +204,14 @@ __device__ __forceinline__ float capped_exponent(float raw, const PrefillParams&
   return raw == -INFINITY ? -INFINITY : s * kLog2eA;
 }
 
-// CAPPED: the scores are soft-capped and chunks bound the visible keys (PrefillParams); the plain instantiation carries
-// none of that code. The cap grows with the score, so a tile's maximum is still found on the raw scores.
-template <bool CAPPED>
+// CAPPED: the scores are soft-capped, get a bias by distance and chunks bound the visible keys (PrefillParams); the plain
+// instantiation carries none of that code. The cap grows with the score, so a tile's maximum is still found on the raw
+// scores; with a bias the offset of the exponents is moved by a bound instead, the capped maximum plus the largest bias
+// of the head (plus the one number that serves a tile wholly beyond the bias's reach): probabilities stay below
+// 2^kSlack as before and fall short of it by the spread of the head's biases at most. The biases themselves are read
+// in the second pass only, and only in tiles within reach.
+// Three instantiations: plain, CAPPED (cap and chunks) and CAPPED with BIASED.
+template <bool CAPPED, bool BIASED>
 __global__ void __launch_bounds__(kThreadsA, 1)
 flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              const PrefillParams p) {
@@ -462,6 +470,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int tok = min(row / p.group, q_len - 1);
     const int pos = first_pos + tok;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int q_head = kv_head * p.group + (row - (row / p.group) * p.group);
+    const float* bias_row = BIASED ? p.bias + static_cast<int64_t>(q_head) * (p.bias_reach + 1) : nullptr;
+    const float bias_peak = bias_row ? __ldg(p.bias_peak + q_head) * kLog2eA : 0.f;
+    const float far_bias = bias_row ? __ldg(bias_row + p.bias_reach) * kLog2eA : 0.f;
     volatile int* next_tile = &row_next[r];
     volatile float* shared_m = &row_m[r];
     float l = 0.f;            // this thread's sum, relative to the offset `seen`
@@ -506,7 +518,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
       }
       const float raw_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float tile_max = CAPPED ? capped_exponent(raw_max, p) : raw_max * p.scale_log2;
+      // Distance of the tile's first key; the whole tile lies beyond the bias's reach when its last key does.
+      const int d0 = pos - tile_start;
+      const bool far = !BIASED || d0 - (kKeys - 1) >= p.bias_reach;
+      const float tile_max = CAPPED ? capped_exponent(raw_max, p) + (far ? far_bias : bias_peak) : raw_max * p.scale_log2;
       // The offset m is only moved when this tile's maximum exceeds it by more than kSlack (in
       // log2 units): probabilities may then be as large as 2^kSlack, which bfloat16 and the
       // 32-bit sums take easily, and in exchange most tiles need no rescaling of the running
@@ -565,10 +580,18 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         for (int i = 0; i < 32; i += 4) {
           float p0, p1, p2, p3;
           if (CAPPED) {
-            p0 = fast_exp2(capped_exponent(__uint_as_float(raw[i]), p) - offset);
-            p1 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 1]), p) - offset);
-            p2 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 2]), p) - offset);
-            p3 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 3]), p) - offset);
+            float b0 = far_bias, b1 = far_bias, b2 = far_bias, b3 = far_bias;
+            if (BIASED && !far) {  // masked columns (distance below zero or keys of another chunk) read inside the table too
+              const int d = d0 - c0 - i;
+              b0 = __ldg(bias_row + min(max(d, 0), p.bias_reach)) * kLog2eA;
+              b1 = __ldg(bias_row + min(max(d - 1, 0), p.bias_reach)) * kLog2eA;
+              b2 = __ldg(bias_row + min(max(d - 2, 0), p.bias_reach)) * kLog2eA;
+              b3 = __ldg(bias_row + min(max(d - 3, 0), p.bias_reach)) * kLog2eA;
+            }
+            p0 = fast_exp2(capped_exponent(__uint_as_float(raw[i]), p) + (b0 - offset));
+            p1 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 1]), p) + (b1 - offset));
+            p2 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 2]), p) + (b2 - offset));
+            p3 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 3]), p) + (b3 - offset));
           } else {
             p0 = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -offset));
             p1 = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -offset));
@@ -686,9 +709,11 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
                                         const int* seq_kv_len, int first_seq, int num_seqs, int max_q_len,
                                         int max_kv_len, int max_pages, int num_pages, int q_heads, int kv_heads,
                                         int head_dim, int page_size, int window, float scale, int value_head, float softcap,
-                                        int chunk, int* err, cudaStream_t stream) {
+                                        const float* bias, const float* bias_peak, int bias_reach, int chunk, int* err,
+                                        cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   B200_REQUIRE(softcap >= 0.f && chunk >= 0, "flash_prefill_tcgen05: bad cap or chunk");
+  B200_REQUIRE(bias == nullptr || (bias_peak != nullptr && bias_reach >= 0), "flash_prefill_tcgen05: a bias by distance comes with its rows' maxima");
   B200_REQUIRE(b200_flash_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_size, max_kv_len),
                "flash_prefill_tcgen05: unsupported shape (heads %d/%d, head_dim %d, page %d, %d keys)", q_heads, kv_heads,
                head_dim, page_size, max_kv_len);
@@ -720,7 +745,10 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   p.softcap = softcap;
   p.cap_twice_inv = softcap > 0.f ? 2.f / softcap : 0.f;
   p.chunk = chunk;
-  const bool capped = softcap > 0.f || chunk > 0;
+  p.bias = bias;
+  p.bias_peak = bias_peak;
+  p.bias_reach = bias_reach;
+  const bool capped = softcap > 0.f || chunk > 0 || bias != nullptr;
   CUtensorMap k_map, v_map;
   const int64_t rows = static_cast<int64_t>(num_pages) * kv_heads * page_size;
   if (arena_map(&k_map, k_arena, rows, p.piece_rows) != 0) return -1;
@@ -728,9 +756,11 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   const size_t smem = (1 + kStagesK + kStagesV) * static_cast<size_t>(kTileBytesA) + kMaxChunks * sizeof(int) + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_prefill_tcgen05_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return b200_fail("flash_prefill_tcgen05: cannot size shared memory (%zu bytes)", smem);
     configured = true;
@@ -738,8 +768,9 @@ B200_API int b200_flash_prefill_tcgen05(const void* q, const void* k_arena, cons
   const int row_blocks = (max_q_len * p.group + kRows - 1) / kRows;
   const dim3 grid(row_blocks, kv_heads, num_seqs);
   const cudaError_t status =
-      capped ? launch_kernel(flash_prefill_tcgen05_kernel<true>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p)
-             : launch_kernel(flash_prefill_tcgen05_kernel<false>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p);
+      bias != nullptr ? launch_kernel(flash_prefill_tcgen05_kernel<true, true>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p)
+      : capped        ? launch_kernel(flash_prefill_tcgen05_kernel<true, false>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p)
+                      : launch_kernel(flash_prefill_tcgen05_kernel<false, false>, grid, dim3(kThreadsA), smem, stream, k_map, v_map, p);
   if (status != cudaSuccess) return b200_fail("flash_prefill_tcgen05: %s", cudaGetErrorString(status));
   return 0;
 }

@@ -30,10 +30,9 @@ def attend(
     value_head: int = -1,
     shape: ops.ScoreShape = ops.NO_SHAPE,
 ) -> None:
-    """``shape``: a soft cap, a bias by distance and a chunk of visible keys (``ops.ScoreShape``); the plain kernel and the
-    mma.sync kernels take all of it, the tcgen05 prefill kernel the cap and the chunks. So prompt portions with a cap or
-    chunks run on tcgen05 where its sizes hold, those with a bias the mma.sync prefill form, and decoded tokens with any
-    shaping the cp.async split-key kernel.
+    """``shape``: a soft cap, a bias by distance and a chunk of visible keys (``ops.ScoreShape``); the plain kernel, the
+    mma.sync kernels and the tcgen05 prefill kernel take it. So shaped prompt portions run on tcgen05 where its sizes hold
+    (heads of 128) and the mma.sync prefill form otherwise, and decoded tokens with any shaping the cp.async split-key kernel.
 
     ``value_head`` >= 0: every query head's weights are applied to the values of that one kv head
     instead of its own (a mixer that mixes weights over heads asks for one such pass per kv head); the
@@ -63,7 +62,7 @@ def attend(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits, value_head=value_head, shape=shape,
         )
-    if ctx.num_seqs > decode_seqs and shape.bias is None and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+    if ctx.num_seqs > decode_seqs and (shape.bias is None or shape.bias_peak is not None) and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
         ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
     ):
         ops.paged_prefill_attention_tcgen05(

@@ -352,12 +352,13 @@ class ScoreShape:
     """What an attention kernel does to a scaled score before the softmax, beyond masking the future: ``softcap``
     (``s <- softcap * tanh(s / softcap)``), ``bias`` (float32 ``[q_heads, reach + 1]`` on the device: the row of the
     query head at ``min(position - key, reach)`` is added after the cap) and ``chunk`` (a query sees only keys from
-    ``floor(position / chunk) * chunk`` on). The plain kernel and the ``mma.sync`` kernels take it, the tcgen05
-    prefill kernel the cap and the chunks."""
+    ``floor(position / chunk) * chunk`` on). The plain kernel, the ``mma.sync`` kernels and the tcgen05 prefill
+    kernel take it (the last wants ``bias_peak`` beside a bias)."""
 
     softcap: float = 0.0
     bias: torch.Tensor | None = None
     chunk: int = 0
+    bias_peak: torch.Tensor | None = None  # float32 [q_heads]: each row's largest entry (the tcgen05 kernel bounds exponents with it)
 
     def __bool__(self) -> bool:
         return bool(self.softcap > 0.0 or self.bias is not None or self.chunk > 0)
@@ -562,9 +563,11 @@ def paged_prefill_attention_tcgen05(
     shape: ScoreShape = NO_SHAPE,
 ) -> torch.Tensor:
     """Prompt-portion attention on tcgen05 / TMEM for requests ``first_seq ..`` of the step. ``value_head`` >= 0:
-    every query head's weights are applied to the values of that kv head. ``shape``: a soft cap and chunks of visible
-    keys (a bias by distance is not taken here)."""
-    _need(shape.bias is None, "tcgen05 attention takes no bias by distance")
+    every query head's weights are applied to the values of that kv head. ``shape``: a soft cap, a bias by distance
+    (with its rows' maxima) and chunks of visible keys."""
+    _need(shape.bias is None or (shape.bias_peak is not None and shape.bias_peak.dtype == torch.float32 and shape.bias_peak.numel() == q_heads),
+          "tcgen05 attention: a bias by distance comes with its rows' maxima, float32 [q_heads]")
+    reach = shape.arguments(q_heads)[2]
     if num_seqs <= 0:
         return out
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "tcgen05 attention is bfloat16 only")
@@ -573,8 +576,8 @@ def paged_prefill_attention_tcgen05(
         "b200_flash_prefill_tcgen05", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
         ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs), c_int(max_q_len),
         c_int(ctx.max_kv_len), c_int(cache.max_pages), c_int(cache.num_pages), c_int(q_heads), c_int(kv_heads),
-        c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale), c_int(value_head), c_float(shape.softcap), c_int(shape.chunk),
-        ptr(ctx.err), ctx.stream,
+        c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale), c_int(value_head), c_float(shape.softcap), ptr(shape.bias), ptr(shape.bias_peak), reach,
+        c_int(shape.chunk), ptr(ctx.err), ctx.stream,
     )
     return out
 

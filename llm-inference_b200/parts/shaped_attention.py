@@ -119,7 +119,8 @@ class ShapedAttention(Part):
             rel = get("rel", f32)
             buckets = distance_buckets(rel.shape[0], self.bias_reach)
             self.bias_table = rel[torch.from_numpy(buckets).to(device)].t().contiguous()
-        self.shape = ops.ScoreShape(self.softcap, self.bias_table, self.chunk)
+        peak = self.bias_table.max(dim=1).values.contiguous() if self.bias_table is not None else None
+        self.shape = ops.ScoreShape(self.softcap, self.bias_table, self.chunk, peak)
         if self.position is not None:
             self.position.load(tensors, dtype, device)
 
