@@ -347,7 +347,7 @@ def test_tensor_core_kernels_against_the_plain_kernel_far_in(case):
 LENGTHS = [1, 2, 3, 9, 31, 70, 150]
 
 
-@pytest.fixture(scope="module", params=["alpha", "beta", "gamma"])
+@pytest.fixture(scope="module", params=["alpha", "beta", "gamma", "delta"])
 def model_case(request, tmp_path_factory):
     config = CONFIGS[request.param]
     weights = draw_weights(config, seed=17 + len(request.param))

@@ -95,7 +95,19 @@ GAMMA = config_of(
     ],
     logit_scale=2.0,
 )
-CONFIGS = {"alpha": ALPHA, "beta": BETA, "gamma": GAMMA}
+# DELTA: sizes that are multiples of nothing in particular (a width of 50, heads of 10 and 14, a latent of 10 + 6, values of 7,
+# an odd vocabulary, expert widths of 18 and 9, a table of 7 rows, chunks of 5, a chunk of one position).
+DELTA = config_of(
+    50, 101,
+    [
+        with_mlp(chunked_layer(heads=3, kv_heads=3, dim=10, scale=0.6, softcap=4.0, chunk=5, rot=(6, 77.0, scaling(1.5, 20, 3.0, 0.7))), moe(experts=3, top=2, ff=18, shared=9)),
+        with_mlp(latent_layer(heads=2, dim=10, rot_dim=6, vdim=7, kv_rank=10, q_rank=5, scale=0.45, base=123.0, scale_rule=scaling(5.0, 16, 2.0, 0.25)), moe(experts=9, top=4, ff=10, shared=None)),
+        with_mlp(biased_layer(heads=5, kv_heads=1, dim=14, vdim=6, scale=0.55, softcap=6.5, bias=(25, 7)), None),
+        with_mlp(chunked_layer(heads=2, kv_heads=1, dim=18, scale=0.5, softcap=None, chunk=1, rot=(2, 9.0, None)), moe(experts=2, top=1, ff=26, shared=5)),
+    ],
+    eps=2e-6, logit_scale=1.75,
+)
+CONFIGS = {"alpha": ALPHA, "beta": BETA, "gamma": GAMMA, "delta": DELTA}
 
 
 def draw_weights(config: dict, seed: int) -> dict[str, torch.Tensor]:
