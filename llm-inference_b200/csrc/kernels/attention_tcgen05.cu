@@ -568,6 +568,15 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kKeys; c0 += 32) {
+        // The biases of the 32 columns are asked for before the scores, so that their way from the cache overlaps the
+        // TMEM load; masked columns (distance below zero, keys of another chunk) read inside the table too.
+        float shift[32];  // bias - offset, in base 2 (the CAPPED forms only)
+        if (CAPPED) {
+          if (BIASED && !far) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) shift[i] = __ldg(bias_row + min(max(d0 - c0 - i, 0), p.bias_reach));
+          }
+        }
         uint32_t raw[32];
         tmem_ld32(s_addr + c0, raw);
         if (needs_mask) {
@@ -575,23 +584,33 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
           for (int i = 0; i < 32; ++i)
             if (c0 + i > rel_hi || c0 + i < rel_lo) raw[i] = 0xff800000u;
         }
+        if (CAPPED) {
+          // Stage by stage over all 32 columns, so that each special-function operation has 31 independent ones beside it.
+#pragma unroll
+          for (int i = 0; i < 32; ++i) shift[i] = BIASED && !far ? fmaf(shift[i], kLog2eA, -offset) : far_bias - offset;
+          float capped[32];
+          if (p.softcap > 0.f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) capped[i] = __expf(__uint_as_float(raw[i]) * p.scale * p.cap_twice_inv);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) capped[i] = p.softcap - __fdividef(2.f * p.softcap, capped[i] + 1.f);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) capped[i] = __uint_as_float(raw[i]) * p.scale;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            raw[i] = __float_as_uint(raw[i] == 0xff800000u ? 0.f : fast_exp2(fmaf(capped[i], kLog2eA, shift[i])));  // a masked score weighs nothing
+        }
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           float p0, p1, p2, p3;
           if (CAPPED) {
-            float b0 = far_bias, b1 = far_bias, b2 = far_bias, b3 = far_bias;
-            if (BIASED && !far) {  // masked columns (distance below zero or keys of another chunk) read inside the table too
-              const int d = d0 - c0 - i;
-              b0 = __ldg(bias_row + min(max(d, 0), p.bias_reach)) * kLog2eA;
-              b1 = __ldg(bias_row + min(max(d - 1, 0), p.bias_reach)) * kLog2eA;
-              b2 = __ldg(bias_row + min(max(d - 2, 0), p.bias_reach)) * kLog2eA;
-              b3 = __ldg(bias_row + min(max(d - 3, 0), p.bias_reach)) * kLog2eA;
-            }
-            p0 = fast_exp2(capped_exponent(__uint_as_float(raw[i]), p) + (b0 - offset));
-            p1 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 1]), p) + (b1 - offset));
-            p2 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 2]), p) + (b2 - offset));
-            p3 = fast_exp2(capped_exponent(__uint_as_float(raw[i + 3]), p) + (b3 - offset));
+            p0 = __uint_as_float(raw[i]);
+            p1 = __uint_as_float(raw[i + 1]);
+            p2 = __uint_as_float(raw[i + 2]);
+            p3 = __uint_as_float(raw[i + 3]);
           } else {
             p0 = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -offset));
             p1 = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -offset));
