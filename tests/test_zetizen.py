@@ -206,7 +206,7 @@ SHAPED = {
     "no cap, no bias": biased_layer(heads=3, kv_heads=3, dim=8, vdim=136, scale=1.0, softcap=None, bias=None),
     "chunked": chunked_layer(),
     "chunked, chunks of 8 (a page), heads of 64 rotated whole": chunked_layer(heads=4, kv_heads=2, dim=64, scale=0.3, softcap=6.0, chunk=8, rot=(64, 1000.0, scaling(4.0, 48, 16.0, 1.0))),
-    "chunked, chunks of 21, heads of 128": chunked_layer(heads=4, kv_heads=4, dim=128, scale=0.2, softcap=20.0, chunk=21, rot=(32, 500000.0, scaling(4.0, 2048, 32.0, 1.0))),
+    "chunked, chunks of 21, heads of 128": chunked_layer(heads=6, kv_heads=3, dim=128, scale=0.2, softcap=20.0, chunk=21, rot=(48, 300000.0, scaling(6.0, 1024, 16.0, 2.0))),
     "chunked, one chunk for all, unscaled frequencies": chunked_layer(heads=2, kv_heads=1, dim=16, scale=0.8, softcap=None, chunk=1000, rot=(4, 10.0, None)),
     "values are keys, nothing else": chunked_layer(heads=3, kv_heads=1, dim=24, scale=0.5, softcap=None, chunk=0, rot=None),
 }
@@ -261,7 +261,7 @@ LATENT = {
     "small": latent_layer(),
     "one head, odd sizes, unscaled": latent_layer(heads=1, dim=6, rot_dim=2, vdim=5, kv_rank=7, q_rank=3, scale=0.9, scale_rule=None),
     "tensor-core sizes": latent_layer(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=32, scale=0.25, base=500.0, scale_rule=scaling(2.0, 40, 8.0, 1.0)),
-    "many heads, wide latent": latent_layer(heads=20, dim=16, rot_dim=32, vdim=24, kv_rank=96, q_rank=50, scale=0.2, base=20000.0, scale_rule=scaling(2.0, 2048, 32.0, 1.0)),
+    "many heads, wide latent": latent_layer(heads=20, dim=16, rot_dim=32, vdim=24, kv_rank=96, q_rank=50, scale=0.2, base=15000.0, scale_rule=scaling(3.0, 1024, 24.0, 1.0)),
 }
 
 
@@ -610,3 +610,10 @@ def test_command_line_tools_take_the_design(tmp_path):
     for result in (from_folder, from_shape):
         line = json.loads(result.stdout.strip().splitlines()[-1])
         assert line["prompt_tokens"] == 5 and len(line["tokens"]) == 6 and all(0 <= t < 8192 for t in line["tokens"])
+    # continuous batching with sampling through the scheduler: six requests of unequal lengths on three slots
+    report = tmp_path / "bench.json"
+    timed = run("llm_inference_b200.cli.benchmark", "--random", "zetizen-small", "--mix", "6", "--mix-prompt-lengths", "20", "90",
+                "--mix-output-lengths", "4", "12", "--max-sequences", "3", "--max-model-length", "256", "--kv-cache-mib", "64", "--warmups", "0",
+                "--repetitions", "1", "--output", str(report))
+    assert timed.returncode == 0, timed.stderr[-2000:]
+    assert report.exists() and json.loads(report.read_text())
