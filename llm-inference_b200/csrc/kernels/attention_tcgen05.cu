@@ -573,8 +573,15 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         float shift[32];  // bias - offset, in base 2 (the CAPPED forms only)
         if (CAPPED) {
           if (BIASED && !far) {
+            const int first = d0 - c0;  // distance of column c0; the columns behind it are nearer by one each
+            if (first <= p.bias_reach && first >= 31) {  // all 32 inside the table: no clamps, one address and fixed offsets
+              const float* at = bias_row + first;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) shift[i] = __ldg(bias_row + min(max(d0 - c0 - i, 0), p.bias_reach));
+              for (int i = 0; i < 32; ++i) shift[i] = __ldg(at - i);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) shift[i] = __ldg(bias_row + min(max(first - i, 0), p.bias_reach));
+            }
           }
         }
         uint32_t raw[32];
